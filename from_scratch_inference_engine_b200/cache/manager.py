@@ -28,12 +28,29 @@ from .pool import OutOfPages, PagePool, StateSlots
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """What one cache entry stores per token: kv_heads x head_dim keys and as many values.
-    window = 0 keeps every key; window = W keeps what a query can still see of the last W."""
+    """What one cache entry stores per token: kv_heads x head_dim keys and kv_heads x value_dim
+    values (value_dim = 0: as wide as the keys).  window = 0 keeps every key; window = W keeps
+    what a query can still see of the last W, and beside them the first `keep_first` tokens of
+    the sequence, which stay visible to every later query."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
+    keep_first: int = 0
+    value_dim: int = 0
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
+
+    def covering(self, other: "CacheNeed") -> "CacheNeed":
+        """The need of an entry that `other` reads as well: the same layout, and kept is what
+        either of the two can still see."""
+        if (self.kv_heads, self.head_dim, self.v_dim) != (other.kv_heads, other.head_dim, other.v_dim):
+            raise ValueError(f"cache layouts differ: {self} and {other}")
+        window = 0 if self.window == 0 or other.window == 0 else max(self.window, other.window)
+        keep = 0 if window == 0 else max(self.keep_first, other.keep_first)
+        return CacheNeed(self.kv_heads, self.head_dim, window, keep, self.value_dim)
 
 
 @dataclass
@@ -238,7 +255,8 @@ class CacheManager:
             # the next query sits at position `length` and sees keys > length - window
             first_needed = handle.length - window + 1
             table = handle.tables[g]
-            for block in range(min(len(table), max(0, first_needed) // self.page_size)):
+            kept = self.blocks_for(group.need.keep_first)       # pages of the kept first tokens
+            for block in range(kept, min(len(table), max(0, first_needed) // self.page_size)):
                 if table[block] >= 0:
                     self._free(g, table[block])
                     table[block] = -1

@@ -13,6 +13,7 @@ import json
 from pathlib import Path
 from typing import Any, Dict, Mapping, Type
 
+from .metulix import MetulixConfig
 from .qwen2 import ConfigError, Qwen2Config
 
 _ARCHITECTURES: Dict[str, Type] = {}
@@ -43,10 +44,12 @@ def architecture_name(data: Mapping[str, Any]) -> str:
     names = data.get("architectures")
     if isinstance(names, (list, tuple)) and names:
         return str(names[0])
+    if isinstance(data.get("architecture"), str):      # some designs name themselves in one string
+        return data["architecture"]
     model_type = str(data.get("model_type", ""))
     if model_type in _MODEL_TYPES:
         return _MODEL_TYPES[model_type]
-    raise ConfigError("config.json names no architecture: neither 'architectures' nor a known "
+    raise ConfigError("config.json names no architecture: neither 'architectures', 'architecture' nor a known "
                       f"'model_type' (registered: {', '.join(registered_architectures())})")
 
 
@@ -74,3 +77,4 @@ def load_config(model_dir) -> Any:
 
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config, model_type="qwen2")
+register_architecture("Metulix", MetulixConfig)

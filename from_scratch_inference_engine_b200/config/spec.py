@@ -38,9 +38,9 @@ class LayerSpec:
     prefix: str                      # e.g. "model.layers.3."
     arrangement: str                 # kind of block, e.g. "prenorm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]     # None: the layer has no feed-forward (arrangements that allow it)
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
     # tensor-name prefixes of the four parts below `prefix`
     mixer_name: str = "mixer."
     feed_forward_name: str = "feed_forward."

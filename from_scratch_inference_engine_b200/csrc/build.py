@@ -42,6 +42,9 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     "gemm_tiles": ("gemm_tiles_tcgen05.cu",),
     # mma.sync product without set-up for steps of few tokens against small matrices
     "gemm_skinny": ("gemm_skinny.cu",),
+    # parts of hybrid decoders: layer norm on a sublayer's output, decaying linear attention over
+    # per-request state, and windowed attention with mixed heads behind a short convolution
+    "hybrid": ("layernorm.cu", "lightning.cu", "talking_attention.cu"),
 }
 # specialisations compiled by build_all() beside the default form of every library
 DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)],

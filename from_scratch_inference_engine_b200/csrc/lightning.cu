@@ -1,0 +1,164 @@
+// Linear attention with a per-head decay ("lightning attention") over per-request state.
+//
+//   q_t, k_t = silu(projected q, k)  [heads, dim]     v_t = silu(projected v)  [heads, vdim]
+//   S_t = decay_h * S_{t-1} + k_t v_t^T               o_t = S_t^T q_t
+//   y_t = T( o_t / sqrt(mean(o_t^2) + eps) * gain * sigmoid(g_t) )      over all heads together
+//
+// The state S [heads, dim, vdim] of a request is 32-bit and lives in its state slot; a step
+// carries it on from where the step before left it, token by token in the order of the
+// sequence, so the result does not depend on how the tokens were cut into steps.  The
+// activations, the decay, the state and the output o are 32-bit whatever the storage type.
+#include "common.cuh"
+
+namespace fsie {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+constexpr int SCAN_COLS = 32;      // value columns of one block
+constexpr int SCAN_GROUPS = 4;     // threads that share a column; thread g owns rows g, g + 4, ...
+constexpr int SCAN_TOKENS = 16;    // tokens staged in shared memory at a time
+
+// grid (column slices, heads, requests), SCAN_COLS * SCAN_GROUPS threads.  Thread (col, grp)
+// keeps S[d][col] for d = grp + 4 i in registers (DPT of them), so a warp reads, for each i,
+// four rows of eight consecutive columns: whole 32-byte sectors.
+template <typename T, int DPT>
+__global__ void lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off,
+                                      int v_off, const int* __restrict__ item_qstart,
+                                      const int* __restrict__ item_qlen,
+                                      const int* __restrict__ item_slots, float* __restrict__ state,
+                                      const float* __restrict__ decay, float* __restrict__ out,
+                                      int heads, int dim, int vdim) {
+    extern __shared__ float staged[];                 // q [TOKENS][dim] | k [TOKENS][dim] | v [TOKENS][COLS]
+    const int item = blockIdx.z, head = blockIdx.y;
+    const int slot = item_slots[item];
+    if (slot < 0) return;                              // a padding entry of a fixed-size batch
+    const int start = item_qstart[item], count = item_qlen[item];
+    const int grp = threadIdx.x & (SCAN_GROUPS - 1), col_local = threadIdx.x / SCAN_GROUPS;
+    const int col = blockIdx.x * SCAN_COLS + col_local;
+    const bool live = col < vdim;
+    float* qs = staged;
+    float* ks = staged + SCAN_TOKENS * dim;
+    float* vs = staged + 2 * SCAN_TOKENS * dim;
+    float* mine = state + (((size_t)slot * heads + head) * dim) * vdim + col;
+    const float lambda = decay[head];
+    float s[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = grp + SCAN_GROUPS * i;
+        s[i] = (live && d < dim) ? mine[(size_t)d * vdim] : 0.f;
+    }
+    for (int t0 = 0; t0 < count; t0 += SCAN_TOKENS) {
+        const int n = min(SCAN_TOKENS, count - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
+            const int t = idx / dim, d = idx - t * dim;
+            const T* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
+            qs[idx] = silu_f(to_float(row[q_off]));
+            ks[idx] = silu_f(to_float(row[k_off]));
+        }
+        for (int idx = threadIdx.x; idx < n * SCAN_COLS; idx += blockDim.x) {
+            const int t = idx / SCAN_COLS, c = idx - t * SCAN_COLS;
+            const int cc = blockIdx.x * SCAN_COLS + c;
+            vs[idx] = cc < vdim ? silu_f(to_float(proj[(size_t)(start + t0 + t) * ld + v_off +
+                                                       head * vdim + cc])) : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < n; ++t) {
+            const float v = vs[t * SCAN_COLS + col_local];
+            const float* q = qs + t * dim;
+            const float* k = ks + t * dim;
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = grp + SCAN_GROUPS * i;
+                if (d < dim) {
+                    s[i] = lambda * s[i] + k[d] * v;
+                    o += s[i] * q[d];
+                }
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (grp == 0 && live)
+                out[(size_t)(start + t0 + t) * heads * vdim + head * vdim + col] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = grp + SCAN_GROUPS * i;
+            if (d < dim) mine[(size_t)d * vdim] = s[i];
+        }
+    }
+}
+
+// One block per token: y = T( o * rsqrt(mean(o^2) + eps) * gain * sigmoid(gate) ).
+template <typename T>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ proj, int ld,
+                                     int g_off, const float* __restrict__ gain, T* __restrict__ y,
+                                     int width, float eps) {
+    __shared__ float scratch[32];
+    const size_t t = blockIdx.x;
+    const float* row = o + t * width;
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) sq += row[c] * row[c];
+    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+    const T* gate = proj + t * ld + g_off;
+    T* yr = y + t * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float g = to_float(gate[c]);
+        yr[c] = from_float<T>(row[c] * inv * gain[c] * (1.0f / (1.0f + expf(-g))));
+    }
+}
+
+}  // namespace fsie
+
+using namespace fsie;
+
+extern "C" {
+
+// proj [tokens, ld] holds q at q_off, k at k_off (heads * dim each) and v at v_off (heads * vdim);
+// state [slots, heads, dim, vdim]; out [tokens, heads * vdim] (float).
+int fsie_lightning_scan(const void* proj, int ld, int q_off, int k_off, int v_off,
+                        const int* item_qstart, const int* item_qlen, const int* item_slots,
+                        int items, float* state, const float* decay, float* out, int heads,
+                        int dim, int vdim, int dtype, cudaStream_t stream) {
+    if (items <= 0) return 0;
+    if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || items > 65535) return ERR_BAD_ARGUMENT;
+    if (dim > SCAN_GROUPS * 64) return ERR_UNSUPPORTED;
+    const dim3 grid((vdim + SCAN_COLS - 1) / SCAN_COLS, heads, items);
+    const int threads = SCAN_COLS * SCAN_GROUPS;
+    const size_t smem = (size_t)(2 * SCAN_TOKENS * dim + SCAN_TOKENS * SCAN_COLS) * sizeof(float);
+    const int per_thread = (dim + SCAN_GROUPS - 1) / SCAN_GROUPS;
+#define FSIE_SCAN(T, DPT)                                                                        \
+    lightning_scan_kernel<T, DPT><<<grid, threads, smem, stream>>>(                              \
+        (const T*)proj, ld, q_off, k_off, v_off, item_qstart, item_qlen, item_slots, state,      \
+        decay, out, heads, dim, vdim)
+#define FSIE_SCAN_BY_SIZE(T)                                                                     \
+    do {                                                                                         \
+        if (per_thread <= 4) FSIE_SCAN(T, 4);                                                    \
+        else if (per_thread <= 8) FSIE_SCAN(T, 8);                                               \
+        else if (per_thread <= 16) FSIE_SCAN(T, 16);                                             \
+        else if (per_thread <= 32) FSIE_SCAN(T, 32);                                             \
+        else FSIE_SCAN(T, 64);                                                                   \
+    } while (0)
+    if (dtype == DTYPE_F32) FSIE_SCAN_BY_SIZE(float);
+    else FSIE_SCAN_BY_SIZE(bf16);
+#undef FSIE_SCAN_BY_SIZE
+#undef FSIE_SCAN
+    return FSIE_LAUNCH_CHECK();
+}
+
+int fsie_gated_rmsnorm(const float* o, const void* proj, int ld, int g_off, const float* gain,
+                       void* y, int tokens, int width, float eps, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (dtype == DTYPE_F32)
+        gated_rmsnorm_kernel<float><<<tokens, threads, 0, stream>>>(o, (const float*)proj, ld, g_off,
+                                                                   gain, (float*)y, width, eps);
+    else
+        gated_rmsnorm_kernel<bf16><<<tokens, threads, 0, stream>>>(o, (const bf16*)proj, ld, g_off,
+                                                                  gain, (bf16*)y, width, eps);
+    return FSIE_LAUNCH_CHECK();
+}
+
+}  // extern "C"

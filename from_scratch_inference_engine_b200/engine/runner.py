@@ -91,7 +91,7 @@ class _DecodeGraph:
         group_tables = [(page, list(t) + [[]] * pad) for t in tables]
         return StepContext(runner.runtime, runner._ring, self.scratch, runner.error,
                            list(token_ids) + [0] * pad, list(range(self.batch)),
-                           [1] * self.batch, list(pos0) + [0] * pad, list(slots) + [0] * pad,
+                           [1] * self.batch, list(pos0) + [0] * pad, list(slots) + [-1] * pad,
                            group_tables, table_width=self.width, out=self.buffer,
                            max_context=self.width * page)
 
@@ -121,8 +121,12 @@ class ModelRunner:
         self.pages: List[torch.Tensor] = []
         for group in self.cache.groups:
             need = group.need
-            self.pages.append(torch.zeros((group.num_pages, len(group.entries), 2, need.kv_heads,
-                                           page_size, need.head_dim), dtype=dtype, device=device))
+            if need.v_dim == need.head_dim:
+                shape = (group.num_pages, len(group.entries), 2, need.kv_heads, page_size, need.head_dim)
+            else:           # values of another width than the keys: [page, entry, keys then values]
+                shape = (group.num_pages, len(group.entries),
+                         need.kv_heads * page_size * (need.head_dim + need.v_dim))
+            self.pages.append(torch.zeros(shape, dtype=dtype, device=device))
         self.states: List[Optional[torch.Tensor]] = []
         for need in model.state_needs():
             self.states.append(None if need is None else torch.zeros(
@@ -134,18 +138,23 @@ class ModelRunner:
                 g, position = self.cache.entry_group[entry]
                 pages = self.pages[g]
                 cache.group = g
-                cache.k_pages = pages[:, position, 0]
-                cache.v_pages = pages[:, position, 1]
+                if pages.dim() == 6:
+                    cache.k_pages = pages[:, position, 0]
+                    cache.v_pages = pages[:, position, 1]
+                    cache.pages, cache.entry_index = pages, position
+                else:
+                    keys = needs[entry].kv_heads * page_size * needs[entry].head_dim
+                    cache.k_pages = pages[:, position, :keys]
+                    cache.v_pages = pages[:, position, keys:]
                 cache.page_stride = pages.stride(0)
-                cache.pages, cache.entry_index = pages, position
             self.layer_caches.append(cache)
         self.error = runtime.error
         self._ring = PinnedRing()
         self._scratch: Dict[str, torch.Tensor] = {}
-        # steps of single tokens replay a captured graph (not for mixers with state of their
-        # own, whose Python-side loops a graph would freeze)
-        self.cuda_graphs = (cuda_graphs and all(s is None for s in self.states)
-                            and getattr(model, "capturable", False))
+        # steps of single tokens replay a captured graph when every part says that it launches
+        # the same kernels whatever the data (a mixer that loops over its state in Python does
+        # not; one whose kernels find the state by the slot numbers on the device does)
+        self.cuda_graphs = cuda_graphs and getattr(model, "capturable", False)
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self._graph_pool = None
         self.vocab_size = model.spec.vocab_size
@@ -277,6 +286,12 @@ class ModelRunner:
         cache = self.cache
         for entry in entries:
             cache.reserve(entry.handle, len(entry.tokens))
+        for entry in entries:
+            if entry.handle.fresh_state:          # first step since the slot was acquired: the
+                entry.handle.fresh_state = False  # state still holds what its last owner left
+                for state in self.states:
+                    if state is not None:
+                        state[entry.handle.slot].zero_()
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
             ran, logits = self._decode_step(entries, device_tokens)
             if ran:
@@ -285,15 +300,11 @@ class ModelRunner:
                 return logits
         token_ids: List[int] = []
         q_start, q_len, pos0, slots, want_rows = [], [], [], [], []
-        fresh_slots = []
         for entry in entries:
             q_start.append(len(token_ids))
             q_len.append(len(entry.tokens))
             pos0.append(entry.handle.length)
             slots.append(entry.handle.slot)
-            if entry.handle.fresh_state:          # first step since the slot was acquired
-                fresh_slots.append(entry.handle.slot)
-                entry.handle.fresh_state = False
             want_rows += [len(token_ids) + w for w in entry.want]
             token_ids += [0] if entry.source_row >= 0 else list(entry.tokens)
         tables = [(cache.page_size, [e.handle.table_array(g) for e in entries])
@@ -301,11 +312,6 @@ class ModelRunner:
         ctx = StepContext(self.runtime, self._ring, self._scratch, self.error, token_ids, q_start,
                           q_len, pos0, slots, tables)
         self._place_device_tokens(ctx, entries, q_start, device_tokens)
-        if fresh_slots and any(s is not None for s in self.states):
-            index = torch.tensor(fresh_slots, dtype=torch.long, device=self.runtime.device)
-            for state in self.states:
-                if state is not None:
-                    state.index_fill_(0, index, 0)
         rows = None
         if want_rows:
             rows = self._ring.stage(np.asarray(want_rows, dtype=np.int32), self.runtime.device)
@@ -335,5 +341,6 @@ class ModelRunner:
                     36: "tcgen05 decode attention: a tile or the softmax never arrived",
                     37: "tcgen05 decode attention: scores or outputs never completed",
                     38: "tcgen05 decode attention: shared memory does not start on a 1,024-byte "
-                        "boundary"}
+                        "boundary",
+                    3: "attention: a visible key lies in a page that was given back"}
             raise DeviceFault(what.get(code, f"device error flag {code}"))

@@ -241,9 +241,13 @@ class Runtime:
                                         self.error)
 
     def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor,
-                      tag: Optional[str] = None) -> torch.Tensor:
+                      tag: Optional[str] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """silu(x @ gate.T) * (x @ up.T) for the stacked weight [gate rows; up rows]: one fused
-        kernel for steps of few tokens, else the library product and the SwiGLU kernel."""
+        kernel for steps of few tokens, else the library product and the SwiGLU kernel.  With a
+        `bias` (stacked like the weight) the product adds it and the SwiGLU kernel follows."""
+        if bias is not None:
+            both = self.linear(x, gate_up, bias, None if tag is None else tag + ".gate_up")
+            return ops.swiglu(both, self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype))
         prepared = self._few_tokens(x, gate_up) if self.dtype is torch.bfloat16 else None
         if prepared is not None and prepared.swiglu:
             return self._few_token_product(prepared, x, None, torch.bfloat16, tag)

@@ -93,9 +93,11 @@ def cache_too_small_for_window(cache: CacheManager) -> str:
     a query sees its last `window` keys, which may straddle one page more than they fill."""
     for index, group in enumerate(cache.groups):
         window = group.need.window
-        if window and group.num_pages < cache.blocks_for(window) + 1:
-            return (f"cache group {index} keeps a window of {window} keys and needs "
-                    f"{cache.blocks_for(window) + 1} pages for one request, it has {group.num_pages}")
+        needed = cache.blocks_for(window) + 1 + cache.blocks_for(group.need.keep_first)
+        if window and group.num_pages < needed:
+            return (f"cache group {index} keeps a window of {window} keys (and the first "
+                    f"{group.need.keep_first}) and needs {needed} pages for one request, it has "
+                    f"{group.num_pages}")
     return ""
 
 

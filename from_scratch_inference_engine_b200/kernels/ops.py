@@ -776,3 +776,225 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _check(core().fsie_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k),
                               _ptr(top_p), _ptr(uniform), _ptr(out), _stream()), "sample")
     return out
+
+
+# ------------------------------------------------------------- parts of hybrid decoders
+_hybrid = None
+
+
+def hybrid():
+    """The library of the hybrid decoders' parts (layer norm on a sublayer's output, decaying
+    linear attention, windowed attention with mixed heads), compiled at first use."""
+    global _hybrid
+    if _hybrid is None:
+        lib = build.load_library("hybrid")
+        i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_add_layernorm.argtypes = [p, p, p, p, p, i, i, f, i, i, p]
+        lib.fsie_cast_rows.argtypes = [p, p, ll, i, p]
+        lib.fsie_lightning_scan.argtypes = [p, i, i, i, i, p, p, p, i, p, p, p, i, i, i, i, p]
+        lib.fsie_gated_rmsnorm.argtypes = [p, p, i, i, p, p, i, i, f, i, p]
+        lib.fsie_conv_norm_rotate.argtypes = [p, i, i, i, p, p, p, p, p, i, p, p, p, i, i, p, p, p,
+                                              ll, i, p, i, i, i, i, i, f, i, p, p]
+        lib.fsie_conv_tails.argtypes = [p, i, p, p, p, i, p, i, i, i, p]
+        lib.fsie_talking_attention_tile_tokens.argtypes = [i]
+        lib.fsie_talking_attention.argtypes = [p, p, p, ll, i, p, i, p, p, i, p, p, p, p, p, p,
+                                               i, i, i, i, i, i, i, f, i, p, p]
+        for name in ("fsie_add_layernorm", "fsie_cast_rows", "fsie_lightning_scan",
+                     "fsie_gated_rmsnorm", "fsie_conv_norm_rotate", "fsie_conv_tails",
+                     "fsie_talking_attention_tile_tokens", "fsie_talking_attention"):
+            getattr(lib, name).restype = i
+        _hybrid = lib
+    return _hybrid
+
+
+def layernorm_rows(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                   rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = LN(x[rows[r]]) * gain in out's dtype; x is the float32 residual stream.
+    LN(v) = (v - mean) / sqrt(mean((v - mean)^2) + eps)."""
+    _need(x, torch.float32, "x")
+    _need(gain, torch.float32, "gain")
+    _need(out, None, "out")
+    width = x.shape[-1]
+    if gain.numel() != width:
+        raise KernelError("layernorm_rows: gain width differs from x")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        count = rows.numel()
+    else:
+        count = x.numel() // width
+    if out.numel() < count * width:
+        raise KernelError("layernorm_rows: out is too small")
+    _check(hybrid().fsie_add_layernorm(_ptr(x), _ptr(rows), _ptr(gain), None, _ptr(out), count,
+                                       width, float(eps), 0, _tag(out.dtype), _stream()),
+           "layernorm_rows")
+    return out
+
+
+def add_layernorm(x: torch.Tensor, delta: torch.Tensor, gain: torch.Tensor, eps: float,
+                  copy: Optional[torch.Tensor]) -> None:
+    """x (float32 residual) += LN(delta) * gain; `copy`, when given, gets the new x in delta's
+    dtype (what the next matrix product reads)."""
+    _need(x, torch.float32, "x")
+    _need(delta, None, "delta")
+    _need(gain, torch.float32, "gain")
+    width = x.shape[-1]
+    count = x.numel() // width
+    if delta.shape[-1] != width or delta.numel() != x.numel() or gain.numel() != width:
+        raise KernelError("add_layernorm: shapes do not fit")
+    if copy is not None:
+        _need(copy, delta.dtype, "copy")
+        if copy.numel() < x.numel():
+            raise KernelError("add_layernorm: copy is too small")
+    _check(hybrid().fsie_add_layernorm(_ptr(delta), None, _ptr(gain), _ptr(x), _ptr(copy), count,
+                                       width, float(eps), 1, _tag(delta.dtype), _stream()),
+           "add_layernorm")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = x (float32) in out's dtype."""
+    _need(x, torch.float32, "x")
+    _need(out, None, "out")
+    if out.numel() < x.numel():
+        raise KernelError("cast_rows: out is too small")
+    _check(hybrid().fsie_cast_rows(_ptr(x), _ptr(out), x.numel(), _tag(out.dtype), _stream()),
+           "cast_rows")
+    return out
+
+
+def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
+                   item_qstart: torch.Tensor, item_qlen: torch.Tensor, item_slots: torch.Tensor,
+                   items: int, state: torch.Tensor, decay: torch.Tensor, out: torch.Tensor,
+                   heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Per request and head, token by token: S = decay * S + silu(k) silu(v)^T, o = S^T silu(q).
+    proj [tokens, ld] holds the projections at the given column offsets; state [slots, heads,
+    dim, vdim] (float32) is read and left updated; out [tokens, heads * vdim] float32."""
+    _need(proj, None, "proj")
+    _need(state, torch.float32, "state")
+    _need(decay, torch.float32, "decay")
+    _need(out, torch.float32, "out")
+    for name, t in (("item_qstart", item_qstart), ("item_qlen", item_qlen), ("item_slots", item_slots)):
+        _need(t, torch.int32, name)
+    tokens, ld = proj.shape
+    if max(q_off, k_off) + heads * dim > ld or v_off + heads * vdim > ld:
+        raise KernelError("lightning_scan: projection rows are narrower than q, k and v")
+    if tuple(state.shape[1:]) != (heads, dim, vdim) or decay.numel() != heads:
+        raise KernelError("lightning_scan: state or decay does not fit the heads")
+    if out.numel() < tokens * heads * vdim:
+        raise KernelError("lightning_scan: out is too small")
+    _check(hybrid().fsie_lightning_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(item_qstart),
+                                        _ptr(item_qlen), _ptr(item_slots), items, _ptr(state),
+                                        _ptr(decay), _ptr(out), heads, dim, vdim, _tag(proj.dtype),
+                                        _stream()), "lightning_scan")
+    return out
+
+
+def gated_rmsnorm(o: torch.Tensor, proj: torch.Tensor, g_off: int, gain: torch.Tensor, eps: float,
+                  out: torch.Tensor) -> torch.Tensor:
+    """out[t] = o[t] * rsqrt(mean(o[t]^2) + eps) * gain * sigmoid(proj[t, g_off:g_off + width])."""
+    _need(o, torch.float32, "o")
+    _need(proj, None, "proj")
+    _need(gain, torch.float32, "gain")
+    _need(out, proj.dtype, "out")
+    tokens, width = o.shape
+    if g_off + width > proj.shape[1] or gain.numel() != width or out.numel() < tokens * width:
+        raise KernelError("gated_rmsnorm: shapes do not fit")
+    _check(hybrid().fsie_gated_rmsnorm(_ptr(o), _ptr(proj), proj.shape[1], g_off, _ptr(gain),
+                                       _ptr(out), tokens, width, float(eps), _tag(proj.dtype),
+                                       _stream()), "gated_rmsnorm")
+    return out
+
+
+def conv_norm_rotate(proj: torch.Tensor, items: int, item_qstart: torch.Tensor,
+                     item_pos0: torch.Tensor, item_slots: torch.Tensor,
+                     tails: Optional[torch.Tensor], conv_w: torch.Tensor, taps: int,
+                     q_gain: torch.Tensor, k_gain: Optional[torch.Tensor], cos_sin: torch.Tensor,
+                     rot_dims: int, slot_of: Optional[torch.Tensor],
+                     k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                     page_stride: int, page_size: int, q_out: torch.Tensor, heads: int,
+                     kv_heads: int, dim: int, vdim: int, has_kv: bool, eps: float,
+                     error: torch.Tensor) -> torch.Tensor:
+    """Causal convolution over time of the projected q | k | v rows (earlier rows of the step, or
+    the request's tail of taps - 1 rows), RMS norm of the whole q and the whole k with gains,
+    rotation of interleaved pairs, per-head RMS of v; q -> q_out (float32), k and v -> pages."""
+    _need(proj, None, "proj")
+    _need(conv_w, torch.float32, "conv_w")
+    _need(q_gain, torch.float32, "q_gain")
+    _need(cos_sin, torch.float32, "cos_sin")
+    _need(q_out, torch.float32, "q_out")
+    for name, t in (("item_qstart", item_qstart), ("item_pos0", item_pos0), ("item_slots", item_slots)):
+        _need(t, torch.int32, name)
+    tokens, ld = proj.shape
+    width = heads * dim + (kv_heads * (dim + vdim) if has_kv else 0)
+    if ld != width or conv_w.shape != (width, taps) or q_gain.numel() != heads * dim:
+        raise KernelError("conv_norm_rotate: projection, taps or gains do not fit")
+    if taps > 1:
+        _need(tails, torch.float32, "tails")
+        if tuple(tails.shape[1:]) != (taps - 1, width):
+            raise KernelError("conv_norm_rotate: tails must be [slots, taps - 1, width]")
+    if rot_dims > 0 and cos_sin.shape[-1] != rot_dims:
+        raise KernelError("conv_norm_rotate: cos/sin table width differs from the rotated size")
+    if has_kv:
+        _need(k_gain, torch.float32, "k_gain")
+        _need(slot_of, torch.int32, "slot_of")
+        if k_pages.dtype is not proj.dtype or v_pages.dtype is not proj.dtype:
+            raise KernelError("conv_norm_rotate: cache dtype differs from the projection dtype")
+    if q_out.numel() < tokens * heads * dim:
+        raise KernelError("conv_norm_rotate: q_out is too small")
+    _check(hybrid().fsie_conv_norm_rotate(
+        _ptr(proj), ld, tokens, items, _ptr(item_qstart), _ptr(item_pos0), _ptr(item_slots),
+        _ptr(tails) if taps > 1 else None, _ptr(conv_w), taps, _ptr(q_gain), _ptr(k_gain),
+        _ptr(cos_sin), cos_sin.shape[0], rot_dims, _ptr(slot_of) if has_kv else None,
+        _ptr(k_pages) if has_kv else None, _ptr(v_pages) if has_kv else None, page_stride,
+        page_size, _ptr(q_out), heads, kv_heads, dim, vdim, int(has_kv), float(eps),
+        _tag(proj.dtype), _ptr(error), _stream()), "conv_norm_rotate")
+    return q_out
+
+
+def conv_tails(proj: torch.Tensor, item_qstart: torch.Tensor, item_qlen: torch.Tensor,
+               item_slots: torch.Tensor, items: int, tails: torch.Tensor, taps: int) -> None:
+    """Leave in every request's tail the projected rows of its last taps - 1 positions."""
+    _need(proj, None, "proj")
+    _need(tails, torch.float32, "tails")
+    width = proj.shape[1]
+    if tuple(tails.shape[1:]) != (taps - 1, width):
+        raise KernelError("conv_tails: tails must be [slots, taps - 1, width]")
+    _check(hybrid().fsie_conv_tails(_ptr(proj), width, _ptr(item_qstart), _ptr(item_qlen),
+                                    _ptr(item_slots), items, _ptr(tails), taps, width,
+                                    _tag(proj.dtype), _stream()), "conv_tails")
+
+
+def talking_attention_tile_tokens(heads: int) -> int:
+    """Consecutive tokens of one request that a block of the mixed-heads attention takes
+    (0: more heads than the kernel holds)."""
+    return int(hybrid().fsie_talking_attention_tile_tokens(int(heads)))
+
+
+def talking_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      page_stride: int, page_size: int, block_tables: torch.Tensor,
+                      tile_item: torch.Tensor, tile_row0: torch.Tensor, num_tiles: int,
+                      item_qstart: torch.Tensor, item_qlen: torch.Tensor, item_pos0: torch.Tensor,
+                      item_slots: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, heads: int,
+                      kv_heads: int, dim: int, vdim: int, window: int, keep_first: int,
+                      tile_tokens: int, scale: float, error: torch.Tensor) -> torch.Tensor:
+    """Softmax attention of q (float32 [tokens, heads * dim]) over the visible keys of the pages
+    (j <= i and (window == 0 or i - j < window or j < keep_first)); the normalised weights of all
+    heads are mixed by `talk` [heads, heads] before head h applies its own to the values of its
+    key/value head.  out [tokens, heads * vdim] in the pages' dtype."""
+    _need(q, torch.float32, "q")
+    _need(talk, torch.float32, "talk")
+    _need(out, k_pages.dtype, "out")
+    for name, t in (("block_tables", block_tables), ("tile_item", tile_item),
+                    ("tile_row0", tile_row0), ("item_qstart", item_qstart),
+                    ("item_qlen", item_qlen), ("item_pos0", item_pos0), ("item_slots", item_slots)):
+        _need(t, torch.int32, name)
+    if v_pages.dtype is not k_pages.dtype:
+        raise KernelError("talking_attention: keys and values differ in dtype")
+    if talk.numel() != heads * heads:
+        raise KernelError("talking_attention: the mixing matrix must be [heads, heads]")
+    _check(hybrid().fsie_talking_attention(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), page_stride, page_size, _ptr(block_tables),
+        block_tables.stride(0), _ptr(tile_item), _ptr(tile_row0), num_tiles, _ptr(item_qstart),
+        _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots), _ptr(talk), _ptr(out), heads, kv_heads,
+        dim, vdim, window, keep_first, tile_tokens, float(scale), _tag(k_pages.dtype),
+        _ptr(error), _stream()), "talking_attention")
+    return out

@@ -7,9 +7,10 @@ from typing import List, Optional
 import torch
 
 from ..config.spec import LayerSpec
+from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import LayerCache, Part, build_part, register_part
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 
 
 @register_part("arrangement", "prenorm")
@@ -47,6 +48,7 @@ class PreNormBlock(Part):
 
     def forward(self, ctx, x: torch.Tensor, delta: Optional[torch.Tensor],
                 cache: LayerCache) -> torch.Tensor:
+        ctx.residual_copy = None      # this block changes x without keeping a copy of it up to date
         # the normed rows are read by the sublayer that follows and by nothing after it
         y = self._normed(self.mixer_norm, x, delta, "prenorm.mixer_in")
         mixed = self.mixer.forward(ctx, y, cache)
@@ -60,3 +62,71 @@ class PreNormBlock(Part):
         if isinstance(norm, RMSNorm):
             return norm.forward(x, delta, tag=tag)
         return norm.forward(x, delta)
+
+
+@register_part("arrangement", "outnorm")
+class OutNormBlock(Part):
+    """x += norm(mixer(x)); x += norm(feed_forward(x)): the norms sit on the sublayers' OUTPUTS
+    and the sublayers read the residual stream itself.  A layer may have no feed-forward.
+
+    The residual stream `x` is float32 and is updated in place by the kernel that norms a
+    sublayer's output.  In bfloat16 that kernel also writes the new x in bfloat16, which is what
+    the next sublayer's matrix product reads (`ctx.residual_copy`); in float32 the sublayers read
+    x directly.  Nothing is left pending: forward returns None.
+    """
+
+    def __init__(self, prefix: str, layer: LayerSpec):
+        self.prefix = prefix
+        self.mixer_norm = build_part("norm", layer.mixer_norm, prefix + layer.mixer_norm_name)
+        self.mixer = build_part("mixer", layer.mixer, prefix + layer.mixer_name)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm,
+                                                prefix + layer.feed_forward_norm_name)
+            self.feed_forward = build_part("feed_forward", layer.feed_forward,
+                                           prefix + layer.feed_forward_name)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not isinstance(norm, LayerNorm):
+                raise TypeError("the outnorm arrangement takes norms that can accumulate into the "
+                                "residual stream (layernorm)")
+
+    def parts(self):
+        return [part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+                                  self.feed_forward) if part is not None]
+
+    @property
+    def capturable(self) -> bool:
+        return all(part.capturable for part in self.parts())
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [spec for part in self.parts() for spec in part.tensor_specs()]
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def _copy_buffer(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        rt = self.runtime
+        if rt.dtype is torch.float32:
+            return None
+        return rt.buffer("outnorm.copy", x.shape[0], x.shape[1], rt.dtype)
+
+    def forward(self, ctx, x: torch.Tensor, delta: Optional[torch.Tensor],
+                cache: LayerCache) -> None:
+        if delta is not None:
+            raise ValueError("outnorm: the block before left a sublayer output pending")
+        copy = self._copy_buffer(x)
+        if copy is None:
+            h = x
+        else:
+            h = getattr(ctx, "residual_copy", None)
+            if h is None:                       # the first block of a model: nobody has cast x yet
+                h = ops.cast_rows(x, copy)
+        mixed = self.mixer.forward(ctx, h, cache)
+        self.mixer_norm.accumulate(x, mixed, copy)
+        if self.feed_forward is not None:
+            out = self.feed_forward.forward(ctx, x if copy is None else copy)
+            self.feed_forward_norm.accumulate(x, out, copy)
+        ctx.residual_copy = copy
+        return None

@@ -86,8 +86,15 @@ class DecoderModel:
             if writes:
                 needs[entry] = need
             elif need != needs[entry]:
-                raise ValueError(f"schedule entry {index} reads cache entry {entry} whose "
-                                 f"layout {needs[entry]} differs from its own {need}")
+                # a reader with another window: the entry keeps what either can still see
+                if need is None or needs[entry] is None:
+                    raise ValueError(f"schedule entry {index} reads cache entry {entry} whose "
+                                     f"layout {needs[entry]} differs from its own {need}")
+                try:
+                    needs[entry] = needs[entry].covering(need)
+                except ValueError as error:
+                    raise ValueError(f"schedule entry {index} reads cache entry {entry}: "
+                                     f"{error}") from None
         return needs
 
     def state_needs(self) -> List[Optional[StateNeed]]:
@@ -103,6 +110,7 @@ class DecoderModel:
         x = rt.buffer("model.residual", ctx.num_tokens, hidden, torch.float32)
         ops.embed_gather(ctx.token_ids, self.embedding, x, ctx.error)
         delta = None
+        ctx.residual_copy = None          # x in the compute dtype, where an arrangement keeps one
         for index, (layer, _, _) in enumerate(self.schedule):
             delta = self.blocks[layer].forward(ctx, x, delta, caches[index])
         if want_rows is None or want_rows.numel() == 0:

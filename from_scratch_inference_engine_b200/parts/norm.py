@@ -1,4 +1,4 @@
-"""RMSNorm fused with the residual add that precedes it."""
+"""Norms: RMSNorm fused with the residual add that precedes it, and layer norm with a gain."""
 
 from __future__ import annotations
 
@@ -39,3 +39,43 @@ class RMSNorm(Part):
         count = x.shape[0] if rows is None else rows.numel()
         out = self.runtime.buffer(tag, count, self.width, self.runtime.dtype)
         return ops.add_rmsnorm(x, delta, self.gain, self.eps, out, rows=rows, write_x=write_x)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * gain over the last axis: a gain and no
+    bias, statistics in 32-bit.  The tensor is `prefix + weight_name`.
+
+    Two uses: `forward` norms rows of the float32 residual stream (a model's final norm);
+    `accumulate` norms a sublayer's output and adds it into the residual stream, for
+    arrangements whose norms sit on the outputs of the sublayers.
+    """
+
+    capturable = True
+
+    def __init__(self, prefix: str, width: int, eps: float, weight_name: str = "weight"):
+        self.prefix, self.width, self.eps = prefix, int(width), float(eps)
+        self.name = prefix + weight_name
+        self.gain: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.name, (self.width,), role="vector", init="gain")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
+        self.runtime = runtime
+        self.gain = tensors[self.name].to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None, write_x: bool = False,
+                tag: Optional[str] = None) -> torch.Tensor:
+        """The normed rows of x (all, or those `rows` names) in the compute dtype."""
+        if delta is not None:
+            raise ValueError("LayerNorm.forward: no pending sublayer output is taken here")
+        count = x.shape[0] if rows is None else rows.numel()
+        out = self.runtime.buffer(tag, count, self.width, self.runtime.dtype)
+        return ops.layernorm_rows(x, self.gain, self.eps, out, rows=rows)
+
+    def accumulate(self, x: torch.Tensor, delta: torch.Tensor,
+                   copy: Optional[torch.Tensor]) -> None:
+        """x += LN(delta) * gain; `copy` (compute dtype) receives the new x when given."""
+        ops.add_layernorm(x, delta, self.gain, self.eps, copy)

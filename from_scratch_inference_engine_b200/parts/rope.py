@@ -23,14 +23,20 @@ def rotary_table(theta: float, rotary_dim: int, length: int) -> np.ndarray:
 
 @register_part("position", "rotary")
 class RotaryEncoding(Part):
-    """Half-rotation pairs (i, i + rotary_dim/2) over the first `rotary_dim` of each head.
-    The rotation itself runs inside the mixer's kernel; this part owns the table."""
+    """Rotation of pairs over the first `rotary_dim` of each head: `pairing` "half" pairs
+    dimension i with i + rotary_dim/2, "interleaved" pairs 2i with 2i + 1; pair i turns by
+    position * theta^(-2i/rotary_dim) either way, so both read the same table.  The rotation
+    itself runs inside the mixer's kernel; this part owns the table and names the pairing."""
 
     capturable = True
 
-    def __init__(self, prefix: str, theta: float, rotary_dim: int, max_position: int = 0):
+    def __init__(self, prefix: str, theta: float, rotary_dim: int, max_position: int = 0,
+                 pairing: str = "half"):
         if rotary_dim % 2:
             raise ValueError("rotary_dim must be even")
+        if pairing not in ("half", "interleaved"):
+            raise ValueError("pairing must be 'half' or 'interleaved'")
+        self.pairing = pairing
         self.prefix, self.theta = prefix, float(theta)
         self.rotary_dim, self.max_position = int(rotary_dim), int(max_position)
         self.table: Optional[torch.Tensor] = None
@@ -39,6 +45,10 @@ class RotaryEncoding(Part):
         self.runtime = runtime
         # as long as the configuration says, and at least as long as the cache can hold
         length = max(self.max_position, runtime.max_positions, 1)
+        if self.rotary_dim == 0:
+            self.table = runtime.shared_table(("rotary-none",),
+                                              lambda: torch.zeros((1, 0), dtype=torch.float32))
+            return
         self.table = runtime.shared_table(
             ("rotary", self.theta, self.rotary_dim, length),
             lambda: torch.from_numpy(rotary_table(self.theta, self.rotary_dim, length)))
