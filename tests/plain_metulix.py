@@ -96,20 +96,22 @@ def causal_conv(u, w):
 def rotate_interleaved(x, heads, dim, rot_dims, base, positions):
     """x [T, heads * dim]: pairs (2i, 2i + 1) of the first rot_dims of each head turn by
     position * base^(-2i / rot_dims)."""
-    out = x.clone().view(len(positions), heads, dim)
-    src = x.view(len(positions), heads, dim)
+    T = len(positions)
+    out = x.clone().view(T, heads, dim)
+    src = x.view(T, heads, dim)
+    pos = torch.tensor(positions, dtype=F64)
     for i in range(rot_dims // 2):
-        f = float(base) ** (-2.0 * i / rot_dims)
-        for t, p in enumerate(positions):
-            c, s = math.cos(p * f), math.sin(p * f)
-            a, b = src[t, :, 2 * i], src[t, :, 2 * i + 1]
-            out[t, :, 2 * i] = a * c - b * s
-            out[t, :, 2 * i + 1] = b * c + a * s
-    return out.reshape(len(positions), heads * dim)
+        angle = pos * float(base) ** (-2.0 * i / rot_dims)
+        c, s = torch.cos(angle)[:, None], torch.sin(angle)[:, None]
+        a, b = src[:, :, 2 * i], src[:, :, 2 * i + 1]
+        out[:, :, 2 * i] = a * c - b * s
+        out[:, :, 2 * i + 1] = b * c + a * s
+    return out.reshape(T, heads * dim)
 
 
 def visible(i, j, size, keep_first):
-    return j <= i and (i - j < size or j < keep_first)
+    """Whether query position i sees key position j (size 0: no window, every earlier key)."""
+    return j <= i and (size <= 0 or i - j < size or j < keep_first)
 
 
 def lightning_recurrence(q, k, v, decay):
@@ -159,14 +161,13 @@ def attention_mixer(h, w, p, m, eps, keys_values=None):
     if keys_values is None:
         keys_values = attention_keys_values(h, w, p, m, eps, positions)
     k, v = keys_values[0].view(T, G, dim), keys_values[1].view(T, G, vdim)
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
+    mask = m.get("mask") or {}
+    size, keep = mask.get("size", 0), mask.get("keep_first", 0)
+    see = torch.tensor([[visible(i, j, size, keep) for j in range(T)] for i in range(T)])
     weights = torch.zeros(H, T, T, dtype=F64)
     for hq in range(H):
-        g = hq // (H // G)
-        for i in range(T):
-            js = [j for j in range(T) if visible(i, j, size, keep)]
-            s = torch.stack([(q[i, hq] * k[j, g]).sum() for j in js]) * m["scale"]
-            weights[hq, i, js] = torch.softmax(s, 0)
+        scores = (q[:, hq] @ k[:, hq // (H // G)].t()) * m["scale"]
+        weights[hq] = torch.softmax(scores.masked_fill(~see, -math.inf), dim=1)
     mixed = torch.einsum("hg,gij->hij", w[p + "talk"], weights)
     out = torch.zeros(T, H, vdim, dtype=F64)
     for hq in range(H):
