@@ -388,6 +388,184 @@ def timeline_workload(args) -> int:
     return 0
 
 
+# sizes of the hybrid comparison: (name, width, heads, kv heads, head size, ff, layers, vocab)
+HYBRID_SIZES = (("w2048", 2048, 16, 4, 128, 8192, 8, 32000),
+                ("w4096", 4096, 32, 8, 128, 14336, 4, 32000))
+
+
+def hybrid_shapes(width, heads, kv_heads, dim, ff, layers, vocab, window, keep_first):
+    """A Metulix model (three lightning layers, then one windowed attention layer, repeated) and
+    the Qwen2 model of equal width, heads, head size, feed-forward, depth, vocabulary and window."""
+    lightning = {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": dim,
+                                                "decay": [1.0 - 2.0 ** -(3 + 5 * h / heads) for h in range(heads)]},
+                 "mlp": {"kind": "dense", "ff": ff}}
+    attention = {"type": "attention", "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": 4, "scale": dim ** -0.5,
+        "rot": {"base": 10000.0, "dims": dim}, "mask": {"size": window, "keep_first": keep_first}},
+        "mlp": {"kind": "dense", "ff": ff}}
+    metulix = {"architecture": "Metulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+               "layers": [attention if i % 4 == 3 else lightning for i in range(layers)]}
+    qwen = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=layers,
+                hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=dim,
+                intermediate_size=ff, vocab_size=vocab, rope_theta=10000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=8192, use_sliding_window=True,
+                sliding_window=window, max_window_layers=0)
+    return metulix, qwen
+
+
+def hybrid_workload(args) -> int:
+    """The Metulix design beside the Qwen2 model of equal size (random bf16 weights): prefill of
+    one prompt and decode steps of a batch, through the same step function, timed on the device
+    with CUDA events; and where the time goes, per kind of kernel, from events around every
+    launch of one prefill step and one decode step (run without graphs for that).  One JSON line."""
+    import numpy as np
+    import torch
+    from from_scratch_inference_engine_b200 import LoadedModel, ModelRunner, StepEntry
+    from from_scratch_inference_engine_b200.config import config_from_dict
+    from from_scratch_inference_engine_b200.kernels import ops
+
+    peak, peak_source = peaks()
+    prompt_len, batch, context, page = args.prefill_tokens, args.batch, args.context, 16
+    window, keep_first = 1024, 4
+    steps, warmup = min(args.steps, 32), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    compute = "bfloat16" if args.dtype in ("bf16", "bfloat16") else "float32"
+
+    def timed(fn):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end)
+
+    kinds = [name for name in ("embed_gather", "add_rmsnorm", "rope_kv_write", "swiglu", "gemm_f32",
+                               "attention_generic", "attention_mma", "attention_tc", "attention_tc_decode",
+                               "gemm_decode", "gemm_skinny", "gemm_skinny_qkv_rope", "gemm_tiles",
+                               "layernorm_rows", "add_layernorm", "cast_rows", "lightning_scan",
+                               "gated_rmsnorm", "conv_norm_rotate", "conv_tails", "talking_attention")
+             if hasattr(ops, name)]
+
+    def by_kind(fn):
+        """ms per kind of kernel of one call of fn: events around every launch through `ops`, and
+        around the library products of the runtime (torch.mm / addmm)."""
+        records, originals = [], {}
+
+        def wrap(name, inner):
+            def outer(*a, **k):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                result = inner(*a, **k)
+                end.record()
+                records.append((name, start, end))
+                return result
+            return outer
+        for name in kinds:
+            originals[name] = getattr(ops, name)
+            setattr(ops, name, wrap(name, originals[name]))
+        library = {name: getattr(torch, name) for name in ("mm", "addmm")}
+        for name, inner in library.items():
+            setattr(torch, name, wrap("library product", inner))
+        try:
+            total = timed(fn)
+        finally:
+            for name, inner in originals.items():
+                setattr(ops, name, inner)
+            for name, inner in library.items():
+                setattr(torch, name, inner)
+        out = {}
+        for name, start, end in records:
+            out[name] = out.get(name, 0.0) + start.elapsed_time(end)
+        out["(whole step)"] = total
+        return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
+
+    sizes = [s for s in HYBRID_SIZES if not args.sizes or s[0] in args.sizes.split(",")]
+    results = []
+    clocks = ClockSampler()
+    clocks.start()
+    for name, width, heads, kv_heads, dim, ff, layers, vocab in sizes:
+        layers = args.layers or layers
+        shapes = hybrid_shapes(width, heads, kv_heads, dim, ff, layers, vocab, window, keep_first)
+        entry = {"size": name, "width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
+                 "ff": ff, "layers": layers, "vocab": vocab, "window": window, "keep_first": keep_first}
+        for design, shape in zip(("metulix", "qwen2"), shapes):
+            config = config_from_dict(shape)
+            model = LoadedModel.from_random(config, seed=0, std=0.02, dtype=compute,
+                                            max_positions=max(context, prompt_len) + 64)
+            device = model.runtime.device
+            # ---- prefill of one prompt (the second run is timed)
+            runner = ModelRunner(model.model, model.runtime, page_size=page,
+                                 num_pages=2 * (prompt_len // page + 2), max_requests=2,
+                                 max_step_tokens=prompt_len)
+            prompt = rng.integers(0, vocab, size=prompt_len).tolist()
+            prefill_ms, prefill_kinds = 0.0, {}
+            for attempt in range(3):
+                handle = runner.cache.open(("p", attempt))
+                run = lambda: runner.step([StepEntry(handle, prompt, [prompt_len - 1])])
+                if attempt == 1:
+                    prefill_ms = timed(run)
+                elif attempt == 2:
+                    prefill_kinds = by_kind(run)
+                else:
+                    run()
+                runner.cache.close(handle)
+            runner.raise_on_device_error()
+            del runner
+            torch.cuda.empty_cache()
+            # ---- decode: contexts reserved, not computed (pages and state hold zeros; the kernels
+            # read and multiply them all the same)
+            results_design = {"prefill_tokens_per_s": prompt_len * 1000.0 / prefill_ms,
+                              "prefill_ms": round(prefill_ms, 3), "prefill_ms_by_kind": prefill_kinds}
+            for graphs in (True, False):
+                runner = ModelRunner(model.model, model.runtime, page_size=page,
+                                     num_pages=batch * (context // page + 1), max_requests=batch,
+                                     cuda_graphs=graphs)
+                start_len = context - (steps + warmup + 1)
+                handles = []
+                for r in range(batch):
+                    handle = runner.cache.open(r)
+                    runner.cache.reserve(handle, start_len)
+                    runner.cache.commit(handle, start_len)
+                    handle.fresh_state = False
+                    handles.append(handle)
+                tokens = rng.integers(0, vocab, size=(steps + warmup + 1, batch))
+                picks = torch.empty(batch, dtype=torch.int32, device=device)
+
+                def step(index):
+                    logits = runner.step([StepEntry(h, [int(tokens[index, b])], [0])
+                                          for b, h in enumerate(handles)])
+                    ops.argmax(logits, picks)
+                if graphs:
+                    for index in range(warmup):
+                        step(index)
+                    ms_step = timed(lambda: [step(warmup + index) for index in range(steps)]) / steps
+                    results_design.update(decode_tokens_per_s=batch * 1000.0 / ms_step,
+                                          decode_ms_per_step=round(ms_step, 4),
+                                          decode_in_graphs=bool(runner.cuda_graphs))
+                else:
+                    step(0)
+                    results_design["decode_ms_by_kind"] = by_kind(lambda: step(1))
+                runner.raise_on_device_error()
+                del runner
+                torch.cuda.empty_cache()
+            entry[design] = results_design
+            del model
+            torch.cuda.empty_cache()
+        results.append(entry)
+    clock_record = clocks.stop()
+    print(json.dumps({
+        "metric": "prefill and decode tokens/s of the Metulix design beside Qwen2 at equal size",
+        "impl": "engine", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "dtype": "bf16" if compute == "bfloat16" else "fp32",
+        "config": {"prefill_tokens": prompt_len, "decode_batch": batch, "decode_context": context,
+                   "kv_page": page, "l2": "inputs larger than L2: every step streams all weights"},
+        "peaks": {"hbm_gbs": peak["hbm_gbs"], "bf16_tflops": peak["bf16_tflops"], "source": peak_source},
+        "sizes": results, "clocks": clock_record,
+        "data": "synthetic: random weights N(0,0.02), uniform random token ids; decode contexts reserved, not computed"}))
+    return 0
+
+
 def reference_arm(args) -> int:
     """The same metric and shape through the unmodified reference engine (built from its own
     sources by baseline/build_reference.py; its CUDA engine, CudaEngine::step, decodes the batch
@@ -467,11 +645,13 @@ def main() -> int:
                              "blocks it falls to instead of sharing it out among all (for measuring that choice)")
     parser.add_argument("--fp32-steps", type=int, default=8,
                         help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline", "hybrid"],
                         help="decode: the default measurement; serving: continuous batching of 256 "
                              "requests at the 1.5B shape; long: the 14B shape, decode at batch 32 with "
                              "8,192-token contexts and chunked prefill of an 8,192-token prompt; "
-                             "timeline: kernel start and end times inside one decode step (text)")
+                             "timeline: kernel start and end times inside one decode step (text); "
+                             "hybrid: the Metulix design beside Qwen2 at equal sizes, prefill and decode")
+    parser.add_argument("--sizes", default="", help="hybrid: which sizes to run (w2048,w4096; '' = all)")
     parser.add_argument("--requests", type=int, default=256)
     parser.add_argument("--step-tokens", type=int, default=2048, help="serving: token budget of one step")
     parser.add_argument("--num-blocks", type=int, default=16384)
@@ -492,6 +672,8 @@ def main() -> int:
         return long_context_workload(args)
     if args.workload == "timeline":
         return timeline_workload(args)
+    if args.workload == "hybrid":
+        return hybrid_workload(args)
 
     import numpy as np
     import torch

@@ -21,31 +21,46 @@ constexpr int SCAN_TOKENS = 16;    // tokens staged in shared memory at a time
 // grid (column slices, heads, requests), SCAN_COLS * SCAN_GROUPS threads.  Thread (col, grp)
 // keeps S[d][col] for d = grp + 4 i in registers (DPT of them), so a warp reads, for each i,
 // four rows of eight consecutive columns: whole 32-byte sectors.
+//
+// A block works on one segment of one request: the whole of its new tokens (seg_item == nullptr:
+// segment z is request z, the state comes from and goes back to the request's slot), or one
+// chunk of them.  Chunks make a long prompt parallel: every chunk first sums its own tokens
+// from a zero state (`chunk_states` receives the sum, nothing else is written), a second kernel
+// chains the sums into the state at every chunk's start, and every chunk then runs again from
+// that state and writes the outputs.
 template <typename T, int DPT>
 __global__ void lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off,
                                       int v_off, const int* __restrict__ item_qstart,
                                       const int* __restrict__ item_qlen,
                                       const int* __restrict__ item_slots, float* __restrict__ state,
                                       const float* __restrict__ decay, float* __restrict__ out,
-                                      int heads, int dim, int vdim) {
+                                      int heads, int dim, int vdim,
+                                      const int* __restrict__ seg_item, const int* __restrict__ seg_row0,
+                                      int seg_tokens, float* __restrict__ chunk_states, int phase) {
     extern __shared__ float staged[];                 // q [TOKENS][dim] | k [TOKENS][dim] | v [TOKENS][COLS]
-    const int item = blockIdx.z, head = blockIdx.y;
+    const int item = seg_item ? seg_item[blockIdx.z] : blockIdx.z, head = blockIdx.y;
     const int slot = item_slots[item];
     if (slot < 0) return;                              // a padding entry of a fixed-size batch
-    const int start = item_qstart[item], count = item_qlen[item];
+    const int row0 = seg_item ? seg_row0[blockIdx.z] : 0;
+    const int start = item_qstart[item] + row0;
+    const int count = seg_item ? min(seg_tokens, item_qlen[item] - row0) : item_qlen[item];
+    // phase 0: from the slot, outputs, back to the slot; 1: from zero, the sum to chunk_states;
+    // 2: from chunk_states (the state at the chunk's start), outputs
+    const bool from_zero = phase == 1, write_out = phase != 1;
     const int grp = threadIdx.x & (SCAN_GROUPS - 1), col_local = threadIdx.x / SCAN_GROUPS;
     const int col = blockIdx.x * SCAN_COLS + col_local;
     const bool live = col < vdim;
     float* qs = staged;
     float* ks = staged + SCAN_TOKENS * dim;
     float* vs = staged + 2 * SCAN_TOKENS * dim;
-    float* mine = state + (((size_t)slot * heads + head) * dim) * vdim + col;
+    float* mine = (phase == 0 ? state + (((size_t)slot * heads + head) * dim) * vdim
+                              : chunk_states + (((size_t)blockIdx.z * heads + head) * dim) * vdim) + col;
     const float lambda = decay[head];
     float s[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = grp + SCAN_GROUPS * i;
-        s[i] = (live && d < dim) ? mine[(size_t)d * vdim] : 0.f;
+        s[i] = (live && d < dim && !from_zero) ? mine[(size_t)d * vdim] : 0.f;
     }
     for (int t0 = 0; t0 < count; t0 += SCAN_TOKENS) {
         const int n = min(SCAN_TOKENS, count - t0);
@@ -53,7 +68,7 @@ __global__ void lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_
         for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
             const int t = idx / dim, d = idx - t * dim;
             const T* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
-            qs[idx] = silu_f(to_float(row[q_off]));
+            if (write_out) qs[idx] = silu_f(to_float(row[q_off]));
             ks[idx] = silu_f(to_float(row[k_off]));
         }
         for (int idx = threadIdx.x; idx < n * SCAN_COLS; idx += blockDim.x) {
@@ -67,28 +82,69 @@ __global__ void lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_
             const float v = vs[t * SCAN_COLS + col_local];
             const float* q = qs + t * dim;
             const float* k = ks + t * dim;
-            float o = 0.f;
+            if (!write_out) {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    const int d = grp + SCAN_GROUPS * i;
+                    if (d < dim) s[i] = lambda * s[i] + k[d] * v;
+                }
+                continue;
+            }
+            float o0 = 0.f, o1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; ++i) {
                 const int d = grp + SCAN_GROUPS * i;
                 if (d < dim) {
                     s[i] = lambda * s[i] + k[d] * v;
-                    o += s[i] * q[d];
+                    if (i & 1) o1 += s[i] * q[d]; else o0 += s[i] * q[d];
                 }
             }
+            float o = o0 + o1;
             o += __shfl_xor_sync(0xffffffffu, o, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
             if (grp == 0 && live)
                 out[(size_t)(start + t0 + t) * heads * vdim + head * vdim + col] = o;
         }
     }
-    if (live) {
+    if (live && phase != 2) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = grp + SCAN_GROUPS * i;
             if (d < dim) mine[(size_t)d * vdim] = s[i];
         }
     }
+}
+
+// Chains the chunks' sums of every request: chunk_states[c] (on entry the sum of chunk c's own
+// tokens from a zero state) becomes the state at the start of chunk c, and the request's slot
+// receives the state after its last chunk.  S_after = decay^len * S_before + sum.  One thread per
+// state element; chunks are listed request by request, in order.
+__global__ void lightning_chain_kernel(const int* __restrict__ item_qlen, const int* __restrict__ item_slots,
+                                       int items, float* __restrict__ state, const float* __restrict__ decay,
+                                       float* __restrict__ chunk_states, int seg_tokens, int heads,
+                                       int dim, int vdim) {
+    const int item = blockIdx.y;
+    const int slot = item_slots[item];
+    if (slot < 0) return;
+    const size_t per_head = (size_t)dim * vdim, per_state = per_head * heads;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per_state) return;
+    int first = 0;                                         // index of this request's first chunk
+    for (int i = 0; i < item; ++i) first += (item_qlen[i] + seg_tokens - 1) / seg_tokens;
+    const int count = item_qlen[item];
+    const int chunks = (count + seg_tokens - 1) / seg_tokens;
+    const float lambda = decay[e / per_head];
+    float s = state[(size_t)slot * per_state + e];
+    for (int c = 0; c < chunks; ++c) {
+        const int len = min(seg_tokens, count - c * seg_tokens);
+        float* at = chunk_states + (size_t)(first + c) * per_state + e;
+        const float sum = *at;
+        *at = s;
+        float power = 1.f;                                 // decay^len by the same products as the scan
+        for (int t = 0; t < len; ++t) power *= lambda;
+        s = power * s + sum;
+    }
+    state[(size_t)slot * per_state + e] = s;
 }
 
 // One block per token: y = T( o * rsqrt(mean(o^2) + eps) * gain * sigmoid(gate) ).
@@ -118,21 +174,29 @@ extern "C" {
 
 // proj [tokens, ld] holds q at q_off, k at k_off (heads * dim each) and v at v_off (heads * vdim);
 // state [slots, heads, dim, vdim]; out [tokens, heads * vdim] (float).
+//
+// With seg_item / seg_row0 (num_segs chunks of seg_tokens tokens, listed request by request) and
+// chunk_states [num_segs, heads, dim, vdim] the requests run chunk-parallel in three launches.
 int fsie_lightning_scan(const void* proj, int ld, int q_off, int k_off, int v_off,
                         const int* item_qstart, const int* item_qlen, const int* item_slots,
                         int items, float* state, const float* decay, float* out, int heads,
-                        int dim, int vdim, int dtype, cudaStream_t stream) {
+                        int dim, int vdim, const int* seg_item, const int* seg_row0, int num_segs,
+                        int seg_tokens, float* chunk_states, int dtype, cudaStream_t stream) {
     if (items <= 0) return 0;
     if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || items > 65535) return ERR_BAD_ARGUMENT;
     if (dim > SCAN_GROUPS * 64) return ERR_UNSUPPORTED;
-    const dim3 grid((vdim + SCAN_COLS - 1) / SCAN_COLS, heads, items);
+    const bool chunked = seg_item != nullptr;
+    if (chunked && (!seg_row0 || !chunk_states || num_segs <= 0 || num_segs > 65535 || seg_tokens <= 0))
+        return ERR_BAD_ARGUMENT;
+    dim3 grid((vdim + SCAN_COLS - 1) / SCAN_COLS, heads, chunked ? num_segs : items);
+    int phase = chunked ? 1 : 0;
     const int threads = SCAN_COLS * SCAN_GROUPS;
     const size_t smem = (size_t)(2 * SCAN_TOKENS * dim + SCAN_TOKENS * SCAN_COLS) * sizeof(float);
     const int per_thread = (dim + SCAN_GROUPS - 1) / SCAN_GROUPS;
 #define FSIE_SCAN(T, DPT)                                                                        \
     lightning_scan_kernel<T, DPT><<<grid, threads, smem, stream>>>(                              \
         (const T*)proj, ld, q_off, k_off, v_off, item_qstart, item_qlen, item_slots, state,      \
-        decay, out, heads, dim, vdim)
+        decay, out, heads, dim, vdim, seg_item, seg_row0, seg_tokens, chunk_states, phase)
 #define FSIE_SCAN_BY_SIZE(T)                                                                     \
     do {                                                                                         \
         if (per_thread <= 4) FSIE_SCAN(T, 4);                                                    \
@@ -143,6 +207,18 @@ int fsie_lightning_scan(const void* proj, int ld, int q_off, int k_off, int v_of
     } while (0)
     if (dtype == DTYPE_F32) FSIE_SCAN_BY_SIZE(float);
     else FSIE_SCAN_BY_SIZE(bf16);
+    if (chunked) {
+        int code = FSIE_LAUNCH_CHECK();
+        if (code) return code;
+        const size_t per_state = (size_t)heads * dim * vdim;
+        lightning_chain_kernel<<<dim3((unsigned)((per_state + 255) / 256), items), 256, 0, stream>>>(
+            item_qlen, item_slots, items, state, decay, chunk_states, seg_tokens, heads, dim, vdim);
+        code = FSIE_LAUNCH_CHECK();
+        if (code) return code;
+        phase = 2;
+        if (dtype == DTYPE_F32) FSIE_SCAN_BY_SIZE(float);
+        else FSIE_SCAN_BY_SIZE(bf16);
+    }
 #undef FSIE_SCAN_BY_SIZE
 #undef FSIE_SCAN
     return FSIE_LAUNCH_CHECK();

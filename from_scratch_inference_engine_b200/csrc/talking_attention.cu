@@ -7,7 +7,7 @@
 //             v_head = u_v,head / sqrt(mean(u_v,head^2) + eps)
 //             q -> a 32-bit buffer; k, v -> the pages of the cache
 //   tails     the last taps - 1 projected rows of every request -> its state slot
-//   attend    s_h(i, j) = (q_h,i . k_g(h),j) * scale  for visible j:
+//   attend    (talking_attention.cuh)  s_h(i, j) = (q_h,i . k_g(h),j) * scale  for visible j:
 //                 j <= i and (window == 0 or i - j < window or j < keep_first)
 //             p_h = softmax_j s_h          p'_h = sum_h' talk[h, h'] p_h'
 //             o_h,i = sum_j p'_h(i, j) v_g(h),j
@@ -158,187 +158,6 @@ __global__ void conv_tails_kernel(const T* __restrict__ proj, int ld, const int*
     }
 }
 
-// ------------------------------------------------------------------------------ attend
-constexpr int TA_KEYS = 64;        // keys of one tile
-constexpr int TA_WARPS = 8;
-constexpr int TA_MAX_ROWS = 64;    // (token, head) rows of one block: 8 per warp
-
-struct TalkingArgs {
-    const float* q; const void* k_pages; const void* v_pages; long long page_stride; int page_size;
-    const int* block_tables; int table_stride; const int* tile_item; const int* tile_row0;
-    const int* item_qstart; const int* item_qlen; const int* item_pos0; const int* item_slots;
-    const float* talk;
-    void* out; int heads, kv_heads, dim, vdim, window, keep_first, tile_tokens; float scale; int* error;
-};
-
-// One block per tile of `tile_tokens` consecutive tokens of one request, all heads: row r =
-// token * heads + head.  Warp w owns rows w, w + 8, ...  The visible keys of the tile are the kept
-// first tokens below the window, then the window of its first token up to its last token; they
-// are walked twice in tiles of TA_KEYS: once for every row's maximum and sum, once to form the
-// normalised weights of all heads, mix them and apply them to the values.
-template <typename T, int VC>
-__global__ void __launch_bounds__(TA_WARPS * 32)
-talking_attention_kernel(const TalkingArgs a) {
-    extern __shared__ float smem[];
-    const int H = a.heads, G = a.kv_heads, dim = a.dim, vdim = a.vdim;
-    const int group = H / G;
-    const int tile = blockIdx.x;
-    const int item = a.tile_item[tile], tok0 = a.tile_row0[tile];
-    if (a.item_slots[item] < 0) return;                 // a padding entry of a fixed-size batch
-    const int qlen = a.item_qlen[item];
-    const int n_tok = min(a.tile_tokens, qlen - tok0);
-    if (n_tok <= 0) return;
-    const int R = n_tok * H;
-    const int p_first = a.item_pos0[item] + tok0, p_last = p_first + n_tok - 1;
-    const int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
-    const int kept = min(a.keep_first, lo);             // kept first tokens that lie below the window
-    const int n_keys = kept + (p_last - lo + 1);
-    const int kv_ld = max(dim, vdim) + 1;
-
-    float* qs = smem;                                   // [rows][dim]
-    float* kv = qs + TA_MAX_ROWS * dim;                 // [TA_KEYS][kv_ld]
-    float* P = kv + TA_KEYS * kv_ld;                    // [rows][TA_KEYS]
-    float* P2 = P + TA_MAX_ROWS * TA_KEYS;              // [rows][TA_KEYS]
-    float* talk = P2 + TA_MAX_ROWS * TA_KEYS;           // [H][H]
-    int* key_page = reinterpret_cast<int*>(talk + H * H);   // [TA_KEYS]
-    int* key_off = key_page + TA_KEYS;                  // [TA_KEYS]
-
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const T* k_pages = reinterpret_cast<const T*>(a.k_pages);
-    const T* v_pages = reinterpret_cast<const T*>(a.v_pages);
-    const int* table = a.block_tables + (size_t)item * a.table_stride;
-
-    const size_t q_row0 = (size_t)(a.item_qstart[item] + tok0) * H * dim;
-    for (int idx = threadIdx.x; idx < R * dim; idx += blockDim.x) qs[idx] = a.q[q_row0 + idx];
-    for (int idx = threadIdx.x; idx < H * H; idx += blockDim.x) talk[idx] = a.talk[idx];
-
-    float row_max[TA_MAX_ROWS / TA_WARPS], row_sum[TA_MAX_ROWS / TA_WARPS];
-    float acc[TA_MAX_ROWS / TA_WARPS][VC];
-#pragma unroll
-    for (int k = 0; k < TA_MAX_ROWS / TA_WARPS; ++k) {
-        row_max[k] = -INFINITY;
-        row_sum[k] = 0.f;
-#pragma unroll
-        for (int c = 0; c < VC; ++c) acc[k][c] = 0.f;
-    }
-
-    for (int pass = 0; pass < 2; ++pass) {
-        for (int u0 = 0; u0 < n_keys; u0 += TA_KEYS) {
-            const int n = min(TA_KEYS, n_keys - u0);
-            __syncthreads();                             // the tile before is done with kv, P, P2
-            if (threadIdx.x < TA_KEYS) {
-                int page = -1, off = 0;
-                if ((int)threadIdx.x < n) {
-                    const int u = u0 + threadIdx.x;
-                    const int j = u < kept ? u : lo + (u - kept);
-                    page = table[j / a.page_size];
-                    off = j - (j / a.page_size) * a.page_size;
-                    if (page < 0) atomicExch(a.error, 3);      // a visible key's page was given back
-                }
-                key_page[threadIdx.x] = page;
-                key_off[threadIdx.x] = off;
-            }
-            for (int g = 0; g < G; ++g) {
-                __syncthreads();                         // key_page is written; kv is free again
-                for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
-                    const int jj = idx / dim, d = idx - jj * dim;
-                    const int page = key_page[jj];
-                    kv[jj * kv_ld + d] = page < 0 ? 0.f : to_float(
-                        k_pages[page * a.page_stride + ((size_t)g * a.page_size + key_off[jj]) * dim + d]);
-                }
-                __syncthreads();
-#pragma unroll
-                for (int k = 0; k < TA_MAX_ROWS / TA_WARPS; ++k) {
-                    const int r = warp + TA_WARPS * k;
-                    if (r >= R) continue;
-                    const int i = r / H, h = r - i * H;
-                    if (h / group != g) continue;
-                    const int p_i = p_first + i;
-                    const float* qr = qs + r * dim;
-                    float s0 = 0.f, s1 = 0.f;
-                    const float* k0 = kv + lane * kv_ld;
-                    const float* k1 = kv + (lane + 32) * kv_ld;
-                    for (int d = 0; d < dim; ++d) {
-                        const float qd = qr[d];
-                        s0 += qd * k0[d];
-                        s1 += qd * k1[d];
-                    }
-                    const int ua = u0 + lane, ub = u0 + lane + 32;
-                    const int ja = ua < kept ? ua : lo + (ua - kept);
-                    const int jb = ub < kept ? ub : lo + (ub - kept);
-                    const bool see_a = lane < n && ja <= p_i &&
-                        (a.window <= 0 || p_i - ja < a.window || ja < a.keep_first);
-                    const bool see_b = lane + 32 < n && jb <= p_i &&
-                        (a.window <= 0 || p_i - jb < a.window || jb < a.keep_first);
-                    s0 = see_a ? s0 * a.scale : -INFINITY;
-                    s1 = see_b ? s1 * a.scale : -INFINITY;
-                    if (pass == 0) {
-                        const float m_new = fmaxf(row_max[k], warp_max(fmaxf(s0, s1)));
-                        if (m_new > -INFINITY) {
-                            const float e = (see_a ? expf(s0 - m_new) : 0.f) + (see_b ? expf(s1 - m_new) : 0.f);
-                            row_sum[k] = row_sum[k] * expf(row_max[k] - m_new) + warp_sum(e);
-                            row_max[k] = m_new;
-                        }
-                    } else {
-                        const float inv = 1.0f / row_sum[k];
-                        P[r * TA_KEYS + lane] = see_a ? expf(s0 - row_max[k]) * inv : 0.f;
-                        P[r * TA_KEYS + lane + 32] = see_b ? expf(s1 - row_max[k]) * inv : 0.f;
-                    }
-                }
-            }
-            if (pass == 0) continue;
-            __syncthreads();                             // P holds every head's weights of this tile
-            for (int idx = threadIdx.x; idx < R * TA_KEYS; idx += blockDim.x) {
-                const int r = idx / TA_KEYS, jj = idx - r * TA_KEYS;
-                const int i = r / H, h = r - i * H;
-                const float* mix = talk + h * H;
-                const float* col = P + (size_t)i * H * TA_KEYS + jj;
-                float m = 0.f;
-                for (int g2 = 0; g2 < H; ++g2) m += mix[g2] * col[g2 * TA_KEYS];
-                P2[idx] = m;
-            }
-            for (int g = 0; g < G; ++g) {
-                __syncthreads();                         // P2 is written; kv is free again
-                for (int idx = threadIdx.x; idx < n * vdim; idx += blockDim.x) {
-                    const int jj = idx / vdim, d = idx - jj * vdim;
-                    const int page = key_page[jj];
-                    kv[jj * kv_ld + d] = page < 0 ? 0.f : to_float(
-                        v_pages[page * a.page_stride + ((size_t)g * a.page_size + key_off[jj]) * vdim + d]);
-                }
-                __syncthreads();
-#pragma unroll
-                for (int k = 0; k < TA_MAX_ROWS / TA_WARPS; ++k) {
-                    const int r = warp + TA_WARPS * k;
-                    if (r >= R) continue;
-                    const int h = r % H;
-                    if (h / group != g) continue;
-                    const float* w = P2 + r * TA_KEYS;
-                    for (int jj = 0; jj < n; ++jj) {
-                        const float p = w[jj];
-                        const float* vr = kv + jj * kv_ld;
-#pragma unroll
-                        for (int c = 0; c < VC; ++c) {
-                            const int col = lane + 32 * c;
-                            if (col < vdim) acc[k][c] += p * vr[col];
-                        }
-                    }
-                }
-            }
-        }
-    }
-    T* out = reinterpret_cast<T*>(a.out) + (size_t)(a.item_qstart[item] + tok0) * H * vdim;
-#pragma unroll
-    for (int k = 0; k < TA_MAX_ROWS / TA_WARPS; ++k) {
-        const int r = warp + TA_WARPS * k;
-        if (r >= R) continue;
-#pragma unroll
-        for (int c = 0; c < VC; ++c) {
-            const int col = lane + 32 * c;
-            if (col < vdim) out[(size_t)r * vdim + col] = from_float<T>(acc[k][c]);
-        }
-    }
-}
-
 }  // namespace fsie
 
 using namespace fsie;
@@ -385,55 +204,6 @@ int fsie_conv_tails(const void* proj, int ld, const int* item_qstart, const int*
     else
         conv_tails_kernel<bf16><<<items, 256, 0, stream>>>((const bf16*)proj, ld, item_qstart,
                                                           item_qlen, item_slots, tails, taps, width);
-    return FSIE_LAUNCH_CHECK();
-}
-
-// Tokens of one tile for a model with `heads` heads (rows of a block: tokens * heads <= 64).
-int fsie_talking_attention_tile_tokens(int heads) {
-    if (heads <= 0 || heads > TA_MAX_ROWS) return 0;
-    const int tokens = TA_MAX_ROWS / heads;
-    return tokens > 16 ? 16 : tokens;
-}
-
-int fsie_talking_attention(const float* q, const void* k_pages, const void* v_pages,
-                           long long page_stride, int page_size, const int* block_tables,
-                           int table_stride, const int* tile_item, const int* tile_row0, int num_tiles,
-                           const int* item_qstart, const int* item_qlen, const int* item_pos0,
-                           const int* item_slots, const float* talk, void* out, int heads, int kv_heads, int dim, int vdim,
-                           int window, int keep_first, int tile_tokens, float scale, int dtype,
-                           int* error, cudaStream_t stream) {
-    if (num_tiles <= 0) return 0;
-    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || tile_tokens <= 0 ||
-        tile_tokens * heads > TA_MAX_ROWS || window < 0 || keep_first < 0)
-        return ERR_BAD_ARGUMENT;
-    if (vdim > 256) return ERR_UNSUPPORTED;
-    const int kv_ld = (dim > vdim ? dim : vdim) + 1;
-    const size_t smem = ((size_t)TA_MAX_ROWS * dim + (size_t)TA_KEYS * kv_ld +
-                         2 * (size_t)TA_MAX_ROWS * TA_KEYS + (size_t)heads * heads) * sizeof(float) +
-                        2 * TA_KEYS * sizeof(int);
-    if (smem > 220 * 1024) return ERR_UNSUPPORTED;
-    TalkingArgs a = {q, k_pages, v_pages, page_stride, page_size, block_tables, table_stride,
-                     tile_item, tile_row0, item_qstart, item_qlen, item_pos0, item_slots, talk, out,
-                     heads,
-                     kv_heads, dim, vdim, window, keep_first, tile_tokens, scale, error};
-    const int vc = (vdim + 31) / 32;
-#define FSIE_ATTEND(T, VC)                                                                       \
-    do {                                                                                         \
-        cudaFuncSetAttribute(talking_attention_kernel<T, VC>,                                    \
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
-        talking_attention_kernel<T, VC><<<num_tiles, TA_WARPS * 32, smem, stream>>>(a);          \
-    } while (0)
-#define FSIE_ATTEND_BY_SIZE(T)                                                                   \
-    do {                                                                                         \
-        if (vc <= 1) FSIE_ATTEND(T, 1);                                                          \
-        else if (vc <= 2) FSIE_ATTEND(T, 2);                                                     \
-        else if (vc <= 4) FSIE_ATTEND(T, 4);                                                     \
-        else FSIE_ATTEND(T, 8);                                                                  \
-    } while (0)
-    if (dtype == DTYPE_F32) FSIE_ATTEND_BY_SIZE(float);
-    else FSIE_ATTEND_BY_SIZE(bf16);
-#undef FSIE_ATTEND_BY_SIZE
-#undef FSIE_ATTEND
     return FSIE_LAUNCH_CHECK();
 }
 

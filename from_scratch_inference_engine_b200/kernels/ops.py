@@ -791,17 +791,19 @@ def hybrid():
         i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
         lib.fsie_add_layernorm.argtypes = [p, p, p, p, p, i, i, f, i, i, p]
         lib.fsie_cast_rows.argtypes = [p, p, ll, i, p]
-        lib.fsie_lightning_scan.argtypes = [p, i, i, i, i, p, p, p, i, p, p, p, i, i, i, i, p]
+        lib.fsie_lightning_scan.argtypes = [p, i, i, i, i, p, p, p, i, p, p, p, i, i, i, p, p, i, i, p, i, p]
         lib.fsie_gated_rmsnorm.argtypes = [p, p, i, i, p, p, i, i, f, i, p]
         lib.fsie_conv_norm_rotate.argtypes = [p, i, i, i, p, p, p, p, p, i, p, p, p, i, i, p, p, p,
                                               ll, i, p, i, i, i, i, i, f, i, p, p]
         lib.fsie_conv_tails.argtypes = [p, i, p, p, p, i, p, i, i, i, p]
         lib.fsie_talking_attention_tile_tokens.argtypes = [i]
+        lib.fsie_talking_attention_key_tile.argtypes = [i, i, i, i, i]
         lib.fsie_talking_attention.argtypes = [p, p, p, ll, i, p, i, p, p, i, p, p, p, p, p, p,
-                                               i, i, i, i, i, i, i, f, i, p, p]
+                                               i, i, i, i, i, i, i, i, f, i, p, p, i, p, p]
         for name in ("fsie_add_layernorm", "fsie_cast_rows", "fsie_lightning_scan",
                      "fsie_gated_rmsnorm", "fsie_conv_norm_rotate", "fsie_conv_tails",
-                     "fsie_talking_attention_tile_tokens", "fsie_talking_attention"):
+                     "fsie_talking_attention_tile_tokens", "fsie_talking_attention_key_tile",
+                     "fsie_talking_attention"):
             getattr(lib, name).restype = i
         _hybrid = lib
     return _hybrid
@@ -864,10 +866,17 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
                    item_qstart: torch.Tensor, item_qlen: torch.Tensor, item_slots: torch.Tensor,
                    items: int, state: torch.Tensor, decay: torch.Tensor, out: torch.Tensor,
-                   heads: int, dim: int, vdim: int) -> torch.Tensor:
+                   heads: int, dim: int, vdim: int, seg_item: Optional[torch.Tensor] = None,
+                   seg_row0: Optional[torch.Tensor] = None, num_segs: int = 0, seg_tokens: int = 0,
+                   chunk_states: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Per request and head, token by token: S = decay * S + silu(k) silu(v)^T, o = S^T silu(q).
     proj [tokens, ld] holds the projections at the given column offsets; state [slots, heads,
-    dim, vdim] (float32) is read and left updated; out [tokens, heads * vdim] float32."""
+    dim, vdim] (float32) is read and left updated; out [tokens, heads * vdim] float32.
+
+    With `seg_item` / `seg_row0` (int32, one entry per chunk of `seg_tokens` tokens, listed
+    request by request) and `chunk_states` (float32, num_segs * heads * dim * vdim at least) the
+    chunks of long prompts run side by side: each sums its own tokens, the sums are chained into
+    the state at every chunk's start, and each chunk runs again from there for its outputs."""
     _need(proj, None, "proj")
     _need(state, torch.float32, "state")
     _need(decay, torch.float32, "decay")
@@ -881,10 +890,17 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
         raise KernelError("lightning_scan: state or decay does not fit the heads")
     if out.numel() < tokens * heads * vdim:
         raise KernelError("lightning_scan: out is too small")
+    if seg_item is not None:
+        _need(seg_item, torch.int32, "seg_item")
+        _need(seg_row0, torch.int32, "seg_row0")
+        _need(chunk_states, torch.float32, "chunk_states")
+        if chunk_states.numel() < num_segs * heads * dim * vdim:
+            raise KernelError("lightning_scan: chunk_states is too small")
     _check(hybrid().fsie_lightning_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(item_qstart),
                                         _ptr(item_qlen), _ptr(item_slots), items, _ptr(state),
-                                        _ptr(decay), _ptr(out), heads, dim, vdim, _tag(proj.dtype),
-                                        _stream()), "lightning_scan")
+                                        _ptr(decay), _ptr(out), heads, dim, vdim, _ptr(seg_item),
+                                        _ptr(seg_row0), num_segs, seg_tokens, _ptr(chunk_states),
+                                        _tag(proj.dtype), _stream()), "lightning_scan")
     return out
 
 
@@ -964,9 +980,15 @@ def conv_tails(proj: torch.Tensor, item_qstart: torch.Tensor, item_qlen: torch.T
 
 
 def talking_attention_tile_tokens(heads: int) -> int:
-    """Consecutive tokens of one request that a block of the mixed-heads attention takes
-    (0: more heads than the kernel holds)."""
+    """Consecutive tokens of one request that a block of the mixed-heads attention takes: 8, 4,
+    2 or 1 as the heads grow (0: more heads than the kernel holds)."""
     return int(hybrid().fsie_talking_attention_tile_tokens(int(heads)))
+
+
+def talking_attention_key_tile(heads: int, kv_heads: int, dim: int, vdim: int,
+                               dtype: torch.dtype) -> int:
+    """Keys that a block of the mixed-heads attention takes at a time (0: sizes do not fit)."""
+    return int(hybrid().fsie_talking_attention_key_tile(heads, kv_heads, dim, vdim, _tag(dtype)))
 
 
 def talking_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -975,11 +997,16 @@ def talking_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       item_qstart: torch.Tensor, item_qlen: torch.Tensor, item_pos0: torch.Tensor,
                       item_slots: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, heads: int,
                       kv_heads: int, dim: int, vdim: int, window: int, keep_first: int,
-                      tile_tokens: int, scale: float, error: torch.Tensor) -> torch.Tensor:
+                      tile_tokens: int, scale: float, error: torch.Tensor, nsplit: int = 1,
+                      part_stats: Optional[torch.Tensor] = None,
+                      part_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Softmax attention of q (float32 [tokens, heads * dim]) over the visible keys of the pages
     (j <= i and (window == 0 or i - j < window or j < keep_first)); the normalised weights of all
     heads are mixed by `talk` [heads, heads] before head h applies its own to the values of its
-    key/value head.  out [tokens, heads * vdim] in the pages' dtype."""
+    key/value head.  out [tokens, heads * vdim] in the pages' dtype.  Tiles are `tile_tokens`
+    consecutive tokens of a request (1, or what `talking_attention_tile_tokens` says); with
+    nsplit > 1 every tile's keys are split over that many blocks (float32 scratch part_stats
+    [tiles * nsplit * 128], part_out [nsplit * tokens * heads * vdim])."""
     _need(q, torch.float32, "q")
     _need(talk, torch.float32, "talk")
     _need(out, k_pages.dtype, "out")
@@ -991,10 +1018,18 @@ def talking_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError("talking_attention: keys and values differ in dtype")
     if talk.numel() != heads * heads:
         raise KernelError("talking_attention: the mixing matrix must be [heads, heads]")
+    tokens = q.shape[0]
+    if nsplit > 1:
+        _need(part_stats, torch.float32, "part_stats")
+        _need(part_out, torch.float32, "part_out")
+        if part_stats.numel() < num_tiles * nsplit * 128 or \
+                part_out.numel() < nsplit * tokens * heads * vdim:
+            raise KernelError("talking_attention: split scratch is too small")
     _check(hybrid().fsie_talking_attention(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), page_stride, page_size, _ptr(block_tables),
         block_tables.stride(0), _ptr(tile_item), _ptr(tile_row0), num_tiles, _ptr(item_qstart),
-        _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots), _ptr(talk), _ptr(out), heads, kv_heads,
-        dim, vdim, window, keep_first, tile_tokens, float(scale), _tag(k_pages.dtype),
-        _ptr(error), _stream()), "talking_attention")
+        _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots), _ptr(talk), _ptr(out), tokens, heads,
+        kv_heads, dim, vdim, window, keep_first, tile_tokens, float(scale), nsplit,
+        _ptr(part_stats), _ptr(part_out), _tag(k_pages.dtype), _ptr(error), _stream()),
+        "talking_attention")
     return out

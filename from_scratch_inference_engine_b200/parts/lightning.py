@@ -24,6 +24,7 @@ class LightningAttention(Mixer):
     """
 
     capturable = True
+    CHUNK_TOKENS = 64          # tokens of one chunk when long prompts run chunk-parallel
 
     NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
 
@@ -66,9 +67,18 @@ class LightningAttention(Mixer):
         tokens = y.shape[0]
         proj = rt.linear(y, self.w_in, None, "lightning.in")
         o = rt.buffer("lightning.o", tokens, self.v_width, torch.float32)
+        chunks = {}
+        if int(ctx.h_qlen.max()) > 2 * self.CHUNK_TOKENS:
+            # long prompts: chunks of every request side by side instead of one block per request
+            # and head walking all its tokens
+            tiles = ctx.attention_tiles(1, self.CHUNK_TOKENS)
+            chunks = dict(seg_item=tiles.item, seg_row0=tiles.row0, num_segs=tiles.count,
+                          seg_tokens=self.CHUNK_TOKENS,
+                          chunk_states=ctx.scratch("lightning.chunk_states",
+                                                   tiles.count * self.heads * self.dim * self.vdim))
         ops.lightning_scan(proj, 0, self.qk_width, 2 * self.qk_width, ctx.item_qstart,
                            ctx.item_qlen, ctx.item_slots, ctx.num_items, cache.state, self.decay, o,
-                           self.heads, self.dim, self.vdim)
+                           self.heads, self.dim, self.vdim, **chunks)
         gated = rt.buffer("lightning.gated", tokens, self.v_width, proj.dtype)
         ops.gated_rmsnorm(o, proj, 2 * self.qk_width + self.v_width, self.gain, self.eps, gated)
         return rt.linear(gated, self.w_o, None, "lightning.out")

@@ -107,6 +107,11 @@ class TalkingWindowAttention(Mixer):
         if self.tile_tokens <= 0:
             raise ValueError(f"talking_window_attention: {self.heads} heads are more than the "
                              f"attention kernel holds in one block")
+        self.key_tile = ops.talking_attention_key_tile(self.heads, self.kv_heads, self.dim,
+                                                       self.vdim, runtime.dtype)
+        if self.key_tile <= 0:
+            raise ValueError("talking_window_attention: these head counts and sizes do not fit "
+                             "the attention kernel's shared memory")
 
     def forward(self, ctx, y: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         rt = self.runtime
@@ -128,11 +133,23 @@ class TalkingWindowAttention(Mixer):
         if self.taps > 1:
             ops.conv_tails(proj, ctx.item_qstart, ctx.item_qlen, ctx.item_slots, ctx.num_items,
                            cache.state, self.taps)
-        tiles = ctx.attention_tiles(1, self.tile_tokens)
+        # a step of single tokens takes tiles of one token, a step with prompt portions the
+        # largest tile a block holds for this many heads
+        tile_tokens = 1 if ctx.num_tokens == ctx.num_items else self.tile_tokens
+        tiles = ctx.attention_tiles(1, tile_tokens)
         out = rt.buffer("talking.out", tokens, self.heads * self.vdim, proj.dtype)
+        # fewer tiles than the GPU has room for blocks: every tile's keys are split over several
+        keys = ctx.max_context if self.window <= 0 else \
+            min(ctx.max_context, self.window + self.keep_first + tile_tokens - 1)
+        nsplit = max(1, min(-(-keys // self.key_tile), 2 * rt.sm_count // max(tiles.count, 1), 32))
+        part_stats = part_out = None
+        if nsplit > 1:
+            part_stats = ctx.scratch("talking.part_stats", tiles.count * nsplit * 128)
+            part_out = ctx.scratch("talking.part_out", nsplit * tokens * self.heads * self.vdim)
         ops.talking_attention(q, cache.k_pages, cache.v_pages, cache.page_stride, group.page_size,
                               group.block_tables, tiles.item, tiles.row0, tiles.count,
                               ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, ctx.item_slots,
                               self.talk, out, self.heads, self.kv_heads, self.dim, self.vdim,
-                              self.window, self.keep_first, self.tile_tokens, self.scale, ctx.error)
+                              self.window, self.keep_first, tile_tokens, self.scale, ctx.error,
+                              nsplit, part_stats, part_out)
         return rt.linear(out, self.w_o, None, "talking.o")
