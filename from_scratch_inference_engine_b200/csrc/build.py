@@ -45,7 +45,7 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     # parts of hybrid decoders: layer norm on a sublayer's output, decaying linear attention over
     # per-request state, and windowed attention with mixed heads behind a short convolution
     "hybrid": ("layernorm.cu", "lightning.cu", "talking_attention.cu", "talking_attention_bf16.cu",
-               "talking_attention_f32.cu"),
+               "talking_attention_f32.cu", "talking_attention_mma.cu"),
 }
 # specialisations compiled by build_all() beside the default form of every library
 DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)],

@@ -800,6 +800,11 @@ def hybrid():
         lib.fsie_talking_attention_key_tile.argtypes = [i, i, i, i, i]
         lib.fsie_talking_attention.argtypes = [p, p, p, ll, i, p, i, p, p, i, p, p, p, p, p, p,
                                                i, i, i, i, i, i, i, i, f, i, p, p, i, p, p]
+        lib.fsie_talking_attention_mma_takes.argtypes = [i, i, i, i]
+        lib.fsie_talking_attention_mma.argtypes = [p, p, p, ll, i, p, i, p, p, i, p, p, p, p, p, p, p,
+                                                   i, i, i, i, i, i, i, f, p, p]
+        lib.fsie_talking_attention_mma_takes.restype = i
+        lib.fsie_talking_attention_mma.restype = i
         for name in ("fsie_add_layernorm", "fsie_cast_rows", "fsie_lightning_scan",
                      "fsie_gated_rmsnorm", "fsie_conv_norm_rotate", "fsie_conv_tails",
                      "fsie_talking_attention_tile_tokens", "fsie_talking_attention_key_tile",
@@ -1032,4 +1037,48 @@ def talking_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         kv_heads, dim, vdim, window, keep_first, tile_tokens, float(scale), nsplit,
         _ptr(part_stats), _ptr(part_out), _tag(k_pages.dtype), _ptr(error), _stream()),
         "talking_attention")
+    return out
+
+
+TALKING_MMA_TILE_TOKENS = 16
+
+
+def talking_attention_mma_takes(heads: int, kv_heads: int, dim: int, vdim: int,
+                                dtype: torch.dtype) -> bool:
+    """Whether the tensor-core form of the mixed-heads attention takes these sizes."""
+    return dtype is torch.bfloat16 and bool(
+        hybrid().fsie_talking_attention_mma_takes(heads, kv_heads, dim, vdim))
+
+
+def talking_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                          page_stride: int, page_size: int, block_tables: torch.Tensor,
+                          tile_item: torch.Tensor, tile_row0: torch.Tensor, num_tiles: int,
+                          item_qstart: torch.Tensor, item_qlen: torch.Tensor,
+                          item_pos0: torch.Tensor, item_slots: torch.Tensor, talk: torch.Tensor,
+                          partial: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int,
+                          dim: int, vdim: int, window: int, keep_first: int, scale: float,
+                          error: torch.Tensor) -> torch.Tensor:
+    """The mixed-heads attention of `talking_attention` for tiles of 16 consecutive tokens on the
+    tensor cores (bfloat16 pages): every (query head, value head) pair as a one-walk attention
+    into `partial` (float32, tokens * heads * kv_heads * vdim), then the mixing of the partial
+    outputs by `talk` into out."""
+    _need(q, torch.float32, "q")
+    _need(talk, torch.float32, "talk")
+    _need(partial, torch.float32, "partial")
+    _need(out, torch.bfloat16, "out")
+    for name, t in (("block_tables", block_tables), ("tile_item", tile_item),
+                    ("tile_row0", tile_row0), ("item_qstart", item_qstart),
+                    ("item_qlen", item_qlen), ("item_pos0", item_pos0), ("item_slots", item_slots)):
+        _need(t, torch.int32, name)
+    if k_pages.dtype is not torch.bfloat16 or v_pages.dtype is not torch.bfloat16:
+        raise KernelError("talking_attention_mma: the cache must be bfloat16")
+    tokens = q.shape[0]
+    if partial.numel() < tokens * heads * kv_heads * vdim or talk.numel() != heads * heads:
+        raise KernelError("talking_attention_mma: scratch or mixing matrix does not fit")
+    _check(hybrid().fsie_talking_attention_mma(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), page_stride, page_size, _ptr(block_tables),
+        block_tables.stride(0), _ptr(tile_item), _ptr(tile_row0), num_tiles, _ptr(item_qstart),
+        _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots), _ptr(talk), _ptr(partial), _ptr(out),
+        tokens, heads, kv_heads, dim, vdim, window, keep_first, float(scale), _ptr(error),
+        _stream()), "talking_attention_mma")
     return out

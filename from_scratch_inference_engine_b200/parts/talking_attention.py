@@ -109,6 +109,10 @@ class TalkingWindowAttention(Mixer):
                              f"attention kernel holds in one block")
         self.key_tile = ops.talking_attention_key_tile(self.heads, self.kv_heads, self.dim,
                                                        self.vdim, runtime.dtype)
+        # bfloat16 prompt portions run on the tensor cores where the sizes allow (`tensor_cores`
+        # may be switched off to measure or test the 32-bit form)
+        self.tensor_cores = ops.talking_attention_mma_takes(self.heads, self.kv_heads, self.dim,
+                                                            self.vdim, runtime.dtype)
         if self.key_tile <= 0:
             raise ValueError("talking_window_attention: these head counts and sizes do not fit "
                              "the attention kernel's shared memory")
@@ -133,11 +137,22 @@ class TalkingWindowAttention(Mixer):
         if self.taps > 1:
             ops.conv_tails(proj, ctx.item_qstart, ctx.item_qlen, ctx.item_slots, ctx.num_items,
                            cache.state, self.taps)
+        out = rt.buffer("talking.out", tokens, self.heads * self.vdim, proj.dtype)
+        if self.tensor_cores and ctx.num_tokens != ctx.num_items:
+            # a step with prompt portions, bfloat16, sizes the tensor-core form takes
+            tiles = ctx.attention_tiles(1, ops.TALKING_MMA_TILE_TOKENS)
+            partial = ctx.scratch("talking.partial", tokens * self.heads * self.kv_heads * self.vdim)
+            ops.talking_attention_mma(q, cache.k_pages, cache.v_pages, cache.page_stride,
+                                      group.page_size, group.block_tables, tiles.item, tiles.row0,
+                                      tiles.count, ctx.item_qstart, ctx.item_qlen, ctx.item_pos0,
+                                      ctx.item_slots, self.talk, partial, out, self.heads,
+                                      self.kv_heads, self.dim, self.vdim, self.window,
+                                      self.keep_first, self.scale, ctx.error)
+            return rt.linear(out, self.w_o, None, "talking.o")
         # a step of single tokens takes tiles of one token, a step with prompt portions the
         # largest tile a block holds for this many heads
         tile_tokens = 1 if ctx.num_tokens == ctx.num_items else self.tile_tokens
         tiles = ctx.attention_tiles(1, tile_tokens)
-        out = rt.buffer("talking.out", tokens, self.heads * self.vdim, proj.dtype)
         # fewer tiles than the GPU has room for blocks: every tile's keys are split over several
         keys = ctx.max_context if self.window <= 0 else \
             min(ctx.max_context, self.window + self.keep_first + tile_tokens - 1)

@@ -59,6 +59,12 @@ CONFIGS = {
         with_mlp(lightning(1, 8, 40, (0.75,)), None),
         with_mlp(attention(4, 4, 16, 8, 1, 16, 25, 18, scale=1.0, kv_from=1), 72),
         with_mlp(attention(8, 1, 8, 8, 2, 0, 33, 2), 64)]),
+    # head sizes that the tensor-core form of the attention takes in bfloat16 (prompt portions),
+    # a reader of layer 0's keys with a wider window
+    "wide": model(150, 128, 1e-6, [
+        with_mlp(attention(4, 2, 64, 64, 3, 32, 40, 5), 160),
+        with_mlp(lightning(2, 16, 32, (0.9, 0.99)), None),
+        with_mlp(attention(4, 2, 64, 64, 2, 32, 70, 3, kv_from=0), 96)]),
     # sizes that are no multiple of eight, a single head, a window of one key
     "odd": model(61, 36, 1e-5, [
         with_mlp(attention(1, 1, 6, 10, 2, 6, 1, 2, scale=0.7), 50),

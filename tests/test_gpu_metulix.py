@@ -219,6 +219,33 @@ def test_hybrid_mixed_batches_reuse_pages_and_slots(tmp_path_factory, dtype, bou
     assert all(free == need // 16 for free in runner.cache.free_pages())
 
 
+def test_tensor_core_attention_against_the_32_bit_form_and_plain(tmp_path_factory):
+    """bfloat16 prompt portions at head size 64 run the tensor-core form (mixing on the output
+    side); the same requests with that form switched off run the 32-bit form.  Both lie within
+    the bfloat16 bound of the plain logits and close to one another; portions start and end
+    inside tiles of 16 tokens, windows end inside tiles, single tokens ride along."""
+    folder = folder_of(tmp_path_factory, "wide", sharpen=False)
+    lengths = {"a": 133, "b": 47, "c": 90}
+    requests = {k: helpers.random_ids(vocab_of("wide"), n, i + 40) for i, (k, n) in enumerate(lengths.items())}
+    steps = helpers.trace_mixed(requests, seed=8, max_live=3) + [
+        dict(s, step=1000 + s["step"]) for s in helpers.trace_whole({k + "~w": v for k, v in requests.items()})]
+    names = dict(requests)
+    names.update({k + "~w": v for k, v in requests.items()})
+    both = []
+    for tensor_cores in (True, False):
+        runner = runner_for(folder, "bfloat16", num_pages=40, max_requests=3)
+        mixers = [block.mixer for block in runner.model.blocks if hasattr(block.mixer, "tensor_cores")]
+        assert len(mixers) == 2 and all(m.tensor_cores for m in mixers)
+        for mixer in mixers:
+            mixer.tensor_cores = tensor_cores
+        rows = helpers.run_trace_in_process(runner, steps)
+        assert_rows(rows, names, folder, BF16_BOUND)
+        both.append(rows)
+    for key, row in both[0].items():
+        other = both[1][key]
+        assert float(np.abs(row - other).max()) <= 3e-2 * max(1.0, float(np.abs(other).max())), key
+
+
 def test_hybrid_long_decoding_through_graphs_and_without(tmp_path_factory):
     """A short prompt, then 150 tokens one by one: the window and the kept first tokens pass
     over decoded tokens, pages are given back on the way, and the decode steps replay captured
