@@ -15,12 +15,20 @@ namespace fsie {
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
 constexpr int SCAN_COLS = 32;      // value columns of one block
-constexpr int SCAN_GROUPS = 4;     // threads that share a column; thread g owns rows g, g + 4, ...
+constexpr int SCAN_ROW_GROUPS = 16;// threads that share four columns; thread r owns rows r DR .. r DR + DR - 1
 constexpr int SCAN_TOKENS = 16;    // tokens staged in shared memory at a time
 
-// grid (column slices, heads, requests), SCAN_COLS * SCAN_GROUPS threads.  Thread (col, grp)
-// keeps S[d][col] for d = grp + 4 i in registers (DPT of them), so a warp reads, for each i,
-// four rows of eight consecutive columns: whole 32-byte sectors.
+// where row d of a staged q or k vector lives: the DR rows of a thread are contiguous (one or
+// more 16-byte loads) and the groups are four floats apart in the banks
+template <int DR> __device__ __forceinline__ int scan_row_at(int d) {
+    constexpr int PAD = DR >= 4 ? DR + 4 : DR;
+    return (d / DR) * PAD + d % DR;
+}
+
+// grid (column slices of 32, heads, segments), 128 threads.  Thread (row group r, column group c)
+// keeps the DR x 4 patch S[r DR + i][4 c + x] in registers: a staged k or q value serves four
+// columns and a v value DR rows, so the arithmetic, not shared memory, sets the pace; the
+// output's sum over the rows is finished by shuffles among the 16 row groups.
 //
 // A block works on one segment of one request: the whole of its new tokens (seg_item == nullptr:
 // segment z is request z, the state comes from and goes back to the request's slot), or one
@@ -28,16 +36,19 @@ constexpr int SCAN_TOKENS = 16;    // tokens staged in shared memory at a time
 // from a zero state (`chunk_states` receives the sum, nothing else is written), a second kernel
 // chains the sums into the state at every chunk's start, and every chunk then runs again from
 // that state and writes the outputs.
-template <typename T, int DPT>
-__global__ void lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off,
-                                      int v_off, const int* __restrict__ item_qstart,
-                                      const int* __restrict__ item_qlen,
-                                      const int* __restrict__ item_slots, float* __restrict__ state,
-                                      const float* __restrict__ decay, float* __restrict__ out,
-                                      int heads, int dim, int vdim,
-                                      const int* __restrict__ seg_item, const int* __restrict__ seg_row0,
-                                      int seg_tokens, float* __restrict__ chunk_states, int phase) {
-    extern __shared__ float staged[];                 // q [TOKENS][dim] | k [TOKENS][dim] | v [TOKENS][COLS]
+template <typename T, int DR>
+__global__ void __launch_bounds__(SCAN_COLS / 4 * SCAN_ROW_GROUPS)
+lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+                      const int* __restrict__ item_qstart, const int* __restrict__ item_qlen,
+                      const int* __restrict__ item_slots, float* __restrict__ state,
+                      const float* __restrict__ decay, float* __restrict__ out, int heads, int dim,
+                      int vdim, const int* __restrict__ seg_item, const int* __restrict__ seg_row0,
+                      int seg_tokens, float* __restrict__ chunk_states, int phase) {
+    constexpr int PAD = DR >= 4 ? DR + 4 : DR;
+    constexpr int ROW_LEN = SCAN_ROW_GROUPS * PAD;
+    __shared__ __align__(16) float qs[SCAN_TOKENS * ROW_LEN];
+    __shared__ __align__(16) float ks[SCAN_TOKENS * ROW_LEN];
+    __shared__ __align__(16) float vs[SCAN_TOKENS * SCAN_COLS];
     const int item = seg_item ? seg_item[blockIdx.z] : blockIdx.z, head = blockIdx.y;
     const int slot = item_slots[item];
     if (slot < 0) return;                              // a padding entry of a fixed-size batch
@@ -47,29 +58,36 @@ __global__ void lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_
     // phase 0: from the slot, outputs, back to the slot; 1: from zero, the sum to chunk_states;
     // 2: from chunk_states (the state at the chunk's start), outputs
     const bool from_zero = phase == 1, write_out = phase != 1;
-    const int grp = threadIdx.x & (SCAN_GROUPS - 1), col_local = threadIdx.x / SCAN_GROUPS;
-    const int col = blockIdx.x * SCAN_COLS + col_local;
-    const bool live = col < vdim;
-    float* qs = staged;
-    float* ks = staged + SCAN_TOKENS * dim;
-    float* vs = staged + 2 * SCAN_TOKENS * dim;
+    const int rg = threadIdx.x & (SCAN_ROW_GROUPS - 1), cg = threadIdx.x / SCAN_ROW_GROUPS;
+    const int col0 = blockIdx.x * SCAN_COLS + cg * 4;
+    const bool wide = (vdim & 3) == 0;                 // rows of the state start on 16 bytes
     float* mine = (phase == 0 ? state + (((size_t)slot * heads + head) * dim) * vdim
-                              : chunk_states + (((size_t)blockIdx.z * heads + head) * dim) * vdim) + col;
+                              : chunk_states + (((size_t)blockIdx.z * heads + head) * dim) * vdim);
     const float lambda = decay[head];
-    float s[DPT];
+    float s[DR][4];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = grp + SCAN_GROUPS * i;
-        s[i] = (live && d < dim && !from_zero) ? mine[(size_t)d * vdim] : 0.f;
+    for (int i = 0; i < DR; ++i) {
+        const int d = rg * DR + i;
+        s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        if (from_zero || d >= dim || col0 >= vdim) continue;
+        const float* at = mine + (size_t)d * vdim + col0;
+        if (wide) {
+            const float4 v = *reinterpret_cast<const float4*>(at);
+            s[i][0] = v.x; s[i][1] = v.y; s[i][2] = v.z; s[i][3] = v.w;
+        } else {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) if (col0 + x < vdim) s[i][x] = at[x];
+        }
     }
     for (int t0 = 0; t0 < count; t0 += SCAN_TOKENS) {
         const int n = min(SCAN_TOKENS, count - t0);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
-            const int t = idx / dim, d = idx - t * dim;
+        for (int idx = threadIdx.x; idx < n * SCAN_ROW_GROUPS * DR; idx += blockDim.x) {
+            const int t = idx / (SCAN_ROW_GROUPS * DR), d = idx - t * (SCAN_ROW_GROUPS * DR);
             const T* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
-            if (write_out) qs[idx] = silu_f(to_float(row[q_off]));
-            ks[idx] = silu_f(to_float(row[k_off]));
+            const int at = t * ROW_LEN + scan_row_at<DR>(d);
+            if (write_out) qs[at] = d < dim ? silu_f(to_float(row[q_off])) : 0.f;
+            ks[at] = d < dim ? silu_f(to_float(row[k_off])) : 0.f;
         }
         for (int idx = threadIdx.x; idx < n * SCAN_COLS; idx += blockDim.x) {
             const int t = idx / SCAN_COLS, c = idx - t * SCAN_COLS;
@@ -79,38 +97,65 @@ __global__ void lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_
         }
         __syncthreads();
         for (int t = 0; t < n; ++t) {
-            const float v = vs[t * SCAN_COLS + col_local];
-            const float* q = qs + t * dim;
-            const float* k = ks + t * dim;
-            if (!write_out) {
+            const float4 v4 = *reinterpret_cast<const float4*>(vs + t * SCAN_COLS + cg * 4);
+            const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+            float kk[DR], qq[DR];
+            const float* kr = ks + t * ROW_LEN + rg * PAD;
+            const float* qr = qs + t * ROW_LEN + rg * PAD;
+            if (DR >= 4) {
 #pragma unroll
-                for (int i = 0; i < DPT; ++i) {
-                    const int d = grp + SCAN_GROUPS * i;
-                    if (d < dim) s[i] = lambda * s[i] + k[d] * v;
+                for (int i = 0; i < DR; i += 4) {
+                    const float4 a = *reinterpret_cast<const float4*>(kr + i);
+                    kk[i] = a.x; kk[i + 1] = a.y; kk[i + 2] = a.z; kk[i + 3] = a.w;
+                    if (write_out) {
+                        const float4 b = *reinterpret_cast<const float4*>(qr + i);
+                        qq[i] = b.x; qq[i + 1] = b.y; qq[i + 2] = b.z; qq[i + 3] = b.w;
+                    }
                 }
-                continue;
-            }
-            float o0 = 0.f, o1 = 0.f;
+            } else {
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = grp + SCAN_GROUPS * i;
-                if (d < dim) {
-                    s[i] = lambda * s[i] + k[d] * v;
-                    if (i & 1) o1 += s[i] * q[d]; else o0 += s[i] * q[d];
+                for (int i = 0; i < DR; ++i) {
+                    kk[i] = kr[i];
+                    if (write_out) qq[i] = qr[i];
                 }
             }
-            float o = o0 + o1;
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (grp == 0 && live)
-                out[(size_t)(start + t0 + t) * heads * vdim + head * vdim + col] = o;
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < DR; ++i)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    s[i][x] = lambda * s[i][x] + kk[i] * v[x];
+                    if (write_out) o[x] += s[i][x] * qq[i];
+                }
+            if (!write_out) continue;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                o[x] += __shfl_xor_sync(0xffffffffu, o[x], 1);
+                o[x] += __shfl_xor_sync(0xffffffffu, o[x], 2);
+                o[x] += __shfl_xor_sync(0xffffffffu, o[x], 4);
+                o[x] += __shfl_xor_sync(0xffffffffu, o[x], 8);
+            }
+            if (rg == 0 && col0 < vdim) {
+                float* dst = out + (size_t)(start + t0 + t) * heads * vdim + head * vdim + col0;
+                if (wide) *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+                else {
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) if (col0 + x < vdim) dst[x] = o[x];
+                }
+            }
         }
     }
-    if (live && phase != 2) {
+    if (phase != 2 && col0 < vdim) {
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-            const int d = grp + SCAN_GROUPS * i;
-            if (d < dim) mine[(size_t)d * vdim] = s[i];
+        for (int i = 0; i < DR; ++i) {
+            const int d = rg * DR + i;
+            if (d >= dim) continue;
+            float* at = mine + (size_t)d * vdim + col0;
+            if (wide) *reinterpret_cast<float4*>(at) = make_float4(s[i][0], s[i][1], s[i][2], s[i][3]);
+            else {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) if (col0 + x < vdim) at[x] = s[i][x];
+            }
         }
     }
 }
@@ -184,26 +229,25 @@ int fsie_lightning_scan(const void* proj, int ld, int q_off, int k_off, int v_of
                         int seg_tokens, float* chunk_states, int dtype, cudaStream_t stream) {
     if (items <= 0) return 0;
     if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || items > 65535) return ERR_BAD_ARGUMENT;
-    if (dim > SCAN_GROUPS * 64) return ERR_UNSUPPORTED;
+    if (dim > SCAN_ROW_GROUPS * 16) return ERR_UNSUPPORTED;
     const bool chunked = seg_item != nullptr;
     if (chunked && (!seg_row0 || !chunk_states || num_segs <= 0 || num_segs > 65535 || seg_tokens <= 0))
         return ERR_BAD_ARGUMENT;
     dim3 grid((vdim + SCAN_COLS - 1) / SCAN_COLS, heads, chunked ? num_segs : items);
     int phase = chunked ? 1 : 0;
-    const int threads = SCAN_COLS * SCAN_GROUPS;
-    const size_t smem = (size_t)(2 * SCAN_TOKENS * dim + SCAN_TOKENS * SCAN_COLS) * sizeof(float);
-    const int per_thread = (dim + SCAN_GROUPS - 1) / SCAN_GROUPS;
+    const int threads = SCAN_COLS / 4 * SCAN_ROW_GROUPS;
+    const int per_thread = (dim + SCAN_ROW_GROUPS - 1) / SCAN_ROW_GROUPS;
 #define FSIE_SCAN(T, DPT)                                                                        \
-    lightning_scan_kernel<T, DPT><<<grid, threads, smem, stream>>>(                              \
+    lightning_scan_kernel<T, DPT><<<grid, threads, 0, stream>>>(                                 \
         (const T*)proj, ld, q_off, k_off, v_off, item_qstart, item_qlen, item_slots, state,      \
         decay, out, heads, dim, vdim, seg_item, seg_row0, seg_tokens, chunk_states, phase)
 #define FSIE_SCAN_BY_SIZE(T)                                                                     \
     do {                                                                                         \
-        if (per_thread <= 4) FSIE_SCAN(T, 4);                                                    \
+        if (per_thread <= 1) FSIE_SCAN(T, 1);                                                    \
+        else if (per_thread <= 2) FSIE_SCAN(T, 2);                                               \
+        else if (per_thread <= 4) FSIE_SCAN(T, 4);                                               \
         else if (per_thread <= 8) FSIE_SCAN(T, 8);                                               \
-        else if (per_thread <= 16) FSIE_SCAN(T, 16);                                             \
-        else if (per_thread <= 32) FSIE_SCAN(T, 32);                                             \
-        else FSIE_SCAN(T, 64);                                                                   \
+        else FSIE_SCAN(T, 16);                                                                   \
     } while (0)
     if (dtype == DTYPE_F32) FSIE_SCAN_BY_SIZE(float);
     else FSIE_SCAN_BY_SIZE(bf16);
