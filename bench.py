@@ -443,7 +443,7 @@ def hybrid_workload(args) -> int:
     kinds = [name for name in ("embed_gather", "add_rmsnorm", "rope_kv_write", "swiglu", "gemm_f32",
                                "attention_generic", "attention_mma", "attention_tc", "attention_tc_decode",
                                "gemm_decode", "gemm_skinny", "gemm_skinny_qkv_rope", "gemm_tiles",
-                               "layernorm_rows", "add_layernorm", "cast_rows", "lightning_scan",
+                               "layernorm_rows", "add_layernorm", "cast_rows", "silu_rows", "lightning_scan",
                                "gated_rmsnorm", "conv_norm_rotate", "conv_tails", "talking_attention",
                                "talking_attention_mma")
              if hasattr(ops, name)]

@@ -17,6 +17,8 @@ __global__ void add_layernorm_kernel(const S* __restrict__ src, const int* __res
                                      T* __restrict__ y, int width, float eps) {
     extern __shared__ float row_cache[];
     __shared__ float scratch[32];
+    grid_dependency_wait();
+    grid_dependents_go();
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
     const S* in = src + s * width;
@@ -47,6 +49,8 @@ __global__ void add_layernorm_kernel(const S* __restrict__ src, const int* __res
 
 template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ y, long long count) {
+    grid_dependency_wait();
+    grid_dependents_go();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count;
          i += (long long)gridDim.x * blockDim.x)
         y[i] = from_float<T>(x[i]);
@@ -68,13 +72,15 @@ int fsie_add_layernorm(const void* src, const int* rows, const float* gain, floa
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return ERR_UNSUPPORTED;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    int code = 0;
 #define FSIE_LN(S, T)                                                                           \
     do {                                                                                        \
         if (smem > 48 * 1024)                                                                   \
             cudaFuncSetAttribute(add_layernorm_kernel<S, T>,                                    \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        add_layernorm_kernel<S, T><<<num_rows, threads, smem, stream>>>(                        \
-            (const S*)src, rows, gain, accumulate ? x : nullptr, (T*)y, width, eps);            \
+        code = launch_dependent(add_layernorm_kernel<S, T>, num_rows, threads, smem, stream,    \
+                                (const S*)src, rows, gain, accumulate ? x : nullptr, (T*)y,      \
+                                width, eps);                                                     \
     } while (0)
     if (dtype == DTYPE_F32) {
         FSIE_LN(float, float);
@@ -84,7 +90,7 @@ int fsie_add_layernorm(const void* src, const int* rows, const float* gain, floa
         FSIE_LN(float, bf16);
     }
 #undef FSIE_LN
-    return FSIE_LAUNCH_CHECK();
+    return code;
 }
 
 int fsie_cast_rows(const float* x, void* y, long long count, int dtype, cudaStream_t stream) {
@@ -93,10 +99,8 @@ int fsie_cast_rows(const float* x, void* y, long long count, int dtype, cudaStre
     const long long wanted = (count + threads - 1) / threads;
     const unsigned blocks = (unsigned)(wanted > 4096 ? 4096 : wanted);
     if (dtype == DTYPE_F32)
-        cast_rows_kernel<float><<<blocks, threads, 0, stream>>>(x, (float*)y, count);
-    else
-        cast_rows_kernel<bf16><<<blocks, threads, 0, stream>>>(x, (bf16*)y, count);
-    return FSIE_LAUNCH_CHECK();
+        return launch_dependent(cast_rows_kernel<float>, blocks, threads, 0, stream, x, (float*)y, count);
+    return launch_dependent(cast_rows_kernel<bf16>, blocks, threads, 0, stream, x, (bf16*)y, count);
 }
 
 }  // extern "C"

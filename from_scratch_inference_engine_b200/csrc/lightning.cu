@@ -6,8 +6,9 @@
 //
 // The state S [heads, dim, vdim] of a request is 32-bit and lives in its state slot; a step
 // carries it on from where the step before left it, token by token in the order of the
-// sequence, so the result does not depend on how the tokens were cut into steps.  The
-// activations, the decay, the state and the output o are 32-bit whatever the storage type.
+// sequence, so the result does not depend on how the tokens were cut into steps beyond rounding
+// (long prompts sum chunk by chunk).  The activations, the decay, the state and the output o are
+// 32-bit whatever the storage type.
 #include "common.cuh"
 
 namespace fsie {
@@ -36,9 +37,9 @@ template <int DR> __device__ __forceinline__ int scan_row_at(int d) {
 // from a zero state (`chunk_states` receives the sum, nothing else is written), a second kernel
 // chains the sums into the state at every chunk's start, and every chunk then runs again from
 // that state and writes the outputs.
-template <typename T, int DR>
+template <int DR>
 __global__ void __launch_bounds__(SCAN_COLS / 4 * SCAN_ROW_GROUPS)
-lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                       const int* __restrict__ item_qstart, const int* __restrict__ item_qlen,
                       const int* __restrict__ item_slots, float* __restrict__ state,
                       const float* __restrict__ decay, float* __restrict__ out, int heads, int dim,
@@ -49,6 +50,8 @@ lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, 
     __shared__ __align__(16) float qs[SCAN_TOKENS * ROW_LEN];
     __shared__ __align__(16) float ks[SCAN_TOKENS * ROW_LEN];
     __shared__ __align__(16) float vs[SCAN_TOKENS * SCAN_COLS];
+    grid_dependency_wait();
+    grid_dependents_go();
     const int item = seg_item ? seg_item[blockIdx.z] : blockIdx.z, head = blockIdx.y;
     const int slot = item_slots[item];
     if (slot < 0) return;                              // a padding entry of a fixed-size batch
@@ -61,6 +64,8 @@ lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, 
     const int rg = threadIdx.x & (SCAN_ROW_GROUPS - 1), cg = threadIdx.x / SCAN_ROW_GROUPS;
     const int col0 = blockIdx.x * SCAN_COLS + cg * 4;
     const bool wide = (vdim & 3) == 0;                 // rows of the state start on 16 bytes
+    // q and k rows of a head start on 16 bytes and end on them: staged four values at a time
+    const bool vec = DR * SCAN_ROW_GROUPS >= 4 && ((dim | ld | q_off | k_off) & 3) == 0;
     float* mine = (phase == 0 ? state + (((size_t)slot * heads + head) * dim) * vdim
                               : chunk_states + (((size_t)blockIdx.z * heads + head) * dim) * vdim);
     const float lambda = decay[head];
@@ -82,18 +87,30 @@ lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, 
     for (int t0 = 0; t0 < count; t0 += SCAN_TOKENS) {
         const int n = min(SCAN_TOKENS, count - t0);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < n * SCAN_ROW_GROUPS * DR; idx += blockDim.x) {
-            const int t = idx / (SCAN_ROW_GROUPS * DR), d = idx - t * (SCAN_ROW_GROUPS * DR);
-            const T* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
-            const int at = t * ROW_LEN + scan_row_at<DR>(d);
-            if (write_out) qs[at] = d < dim ? silu_f(to_float(row[q_off])) : 0.f;
-            ks[at] = d < dim ? silu_f(to_float(row[k_off])) : 0.f;
+        if (vec) {
+            constexpr int CHUNKS = SCAN_ROW_GROUPS * DR / 4 > 0 ? SCAN_ROW_GROUPS * DR / 4 : 1;
+            for (int idx = threadIdx.x; idx < n * CHUNKS; idx += blockDim.x) {
+                const int t = idx / CHUNKS, d = (idx - t * CHUNKS) * 4;
+                const float* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
+                const int at = t * ROW_LEN + scan_row_at<DR>(d);
+                const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (write_out)
+                    *reinterpret_cast<float4*>(qs + at) = d < dim ? *reinterpret_cast<const float4*>(row + q_off) : zero;
+                *reinterpret_cast<float4*>(ks + at) = d < dim ? *reinterpret_cast<const float4*>(row + k_off) : zero;
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < n * SCAN_ROW_GROUPS * DR; idx += blockDim.x) {
+                const int t = idx / (SCAN_ROW_GROUPS * DR), d = idx - t * (SCAN_ROW_GROUPS * DR);
+                const float* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
+                const int at = t * ROW_LEN + scan_row_at<DR>(d);
+                if (write_out) qs[at] = d < dim ? row[q_off] : 0.f;
+                ks[at] = d < dim ? row[k_off] : 0.f;
+            }
         }
         for (int idx = threadIdx.x; idx < n * SCAN_COLS; idx += blockDim.x) {
             const int t = idx / SCAN_COLS, c = idx - t * SCAN_COLS;
             const int cc = blockIdx.x * SCAN_COLS + c;
-            vs[idx] = cc < vdim ? silu_f(to_float(proj[(size_t)(start + t0 + t) * ld + v_off +
-                                                       head * vdim + cc])) : 0.f;
+            vs[idx] = cc < vdim ? proj[(size_t)(start + t0 + t) * ld + v_off + head * vdim + cc] : 0.f;
         }
         __syncthreads();
         for (int t = 0; t < n; ++t) {
@@ -160,6 +177,22 @@ lightning_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, 
     }
 }
 
+// act[t, c] = silu(proj[t, c]) for the first `width` columns (q, k and v), widened to 32-bit: the
+// scan reads every value several times (once per column slice and walk), the activation is
+// taken once.
+template <typename T>
+__global__ void silu_rows_kernel(const T* __restrict__ proj, int ld, int width, float* __restrict__ act,
+                                 long long count) {
+    grid_dependency_wait();
+    grid_dependents_go();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / width;
+        const int c = (int)(i - t * width);
+        act[i] = silu_f(to_float(proj[t * ld + c]));
+    }
+}
+
 // Chains the chunks' sums of every request: chunk_states[c] (on entry the sum of chunk c's own
 // tokens from a zero state) becomes the state at the start of chunk c, and the request's slot
 // receives the state after its last chunk.  S_after = decay^len * S_before + sum.  One thread per
@@ -198,6 +231,8 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const T* __res
                                      int g_off, const float* __restrict__ gain, T* __restrict__ y,
                                      int width, float eps) {
     __shared__ float scratch[32];
+    grid_dependency_wait();
+    grid_dependents_go();
     const size_t t = blockIdx.x;
     const float* row = o + t * width;
     float sq = 0.f;
@@ -217,16 +252,30 @@ using namespace fsie;
 
 extern "C" {
 
-// proj [tokens, ld] holds q at q_off, k at k_off (heads * dim each) and v at v_off (heads * vdim);
-// state [slots, heads, dim, vdim]; out [tokens, heads * vdim] (float).
+int fsie_silu_rows(const void* proj, int ld, int width, float* act, int tokens, int dtype,
+                   cudaStream_t stream) {
+    const long long count = (long long)tokens * width;
+    if (count <= 0) return 0;
+    const long long wanted = (count + 255) / 256;
+    const unsigned blocks = (unsigned)(wanted > 8192 ? 8192 : wanted);
+    if (dtype == DTYPE_F32)
+        return launch_dependent(silu_rows_kernel<float>, blocks, 256, 0, stream, (const float*)proj, ld,
+                                width, act, count);
+    return launch_dependent(silu_rows_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)proj, ld, width,
+                            act, count);
+}
+
+// proj [tokens, ld] (float: the activations that fsie_silu_rows left) holds q at q_off, k at k_off
+// (heads * dim each) and v at v_off (heads * vdim); state [slots, heads, dim, vdim]; out [tokens,
+// heads * vdim] (float).
 //
 // With seg_item / seg_row0 (num_segs chunks of seg_tokens tokens, listed request by request) and
 // chunk_states [num_segs, heads, dim, vdim] the requests run chunk-parallel in three launches.
-int fsie_lightning_scan(const void* proj, int ld, int q_off, int k_off, int v_off,
+int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_off,
                         const int* item_qstart, const int* item_qlen, const int* item_slots,
                         int items, float* state, const float* decay, float* out, int heads,
                         int dim, int vdim, const int* seg_item, const int* seg_row0, int num_segs,
-                        int seg_tokens, float* chunk_states, int dtype, cudaStream_t stream) {
+                        int seg_tokens, float* chunk_states, cudaStream_t stream) {
     if (items <= 0) return 0;
     if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || items > 65535) return ERR_BAD_ARGUMENT;
     if (dim > SCAN_ROW_GROUPS * 16) return ERR_UNSUPPORTED;
@@ -237,9 +286,10 @@ int fsie_lightning_scan(const void* proj, int ld, int q_off, int k_off, int v_of
     int phase = chunked ? 1 : 0;
     const int threads = SCAN_COLS / 4 * SCAN_ROW_GROUPS;
     const int per_thread = (dim + SCAN_ROW_GROUPS - 1) / SCAN_ROW_GROUPS;
+    int launch_code = 0;
 #define FSIE_SCAN(T, DPT)                                                                        \
-    lightning_scan_kernel<T, DPT><<<grid, threads, 0, stream>>>(                                 \
-        (const T*)proj, ld, q_off, k_off, v_off, item_qstart, item_qlen, item_slots, state,      \
+    launch_code = launch_dependent(lightning_scan_kernel<DPT>, grid, threads, 0, stream,         \
+        proj, ld, q_off, k_off, v_off, item_qstart, item_qlen, item_slots, state,      \
         decay, out, heads, dim, vdim, seg_item, seg_row0, seg_tokens, chunk_states, phase)
 #define FSIE_SCAN_BY_SIZE(T)                                                                     \
     do {                                                                                         \
@@ -249,23 +299,21 @@ int fsie_lightning_scan(const void* proj, int ld, int q_off, int k_off, int v_of
         else if (per_thread <= 8) FSIE_SCAN(T, 8);                                               \
         else FSIE_SCAN(T, 16);                                                                   \
     } while (0)
-    if (dtype == DTYPE_F32) FSIE_SCAN_BY_SIZE(float);
-    else FSIE_SCAN_BY_SIZE(bf16);
+    FSIE_SCAN_BY_SIZE(float);
+    if (launch_code) return launch_code;
     if (chunked) {
-        int code = FSIE_LAUNCH_CHECK();
-        if (code) return code;
+        int code;
         const size_t per_state = (size_t)heads * dim * vdim;
         lightning_chain_kernel<<<dim3((unsigned)((per_state + 255) / 256), items), 256, 0, stream>>>(
             item_qlen, item_slots, items, state, decay, chunk_states, seg_tokens, heads, dim, vdim);
         code = FSIE_LAUNCH_CHECK();
         if (code) return code;
         phase = 2;
-        if (dtype == DTYPE_F32) FSIE_SCAN_BY_SIZE(float);
-        else FSIE_SCAN_BY_SIZE(bf16);
+        FSIE_SCAN_BY_SIZE(float);
     }
 #undef FSIE_SCAN_BY_SIZE
 #undef FSIE_SCAN
-    return FSIE_LAUNCH_CHECK();
+    return launch_code;
 }
 
 int fsie_gated_rmsnorm(const float* o, const void* proj, int ld, int g_off, const float* gain,
@@ -273,12 +321,10 @@ int fsie_gated_rmsnorm(const float* o, const void* proj, int ld, int g_off, cons
     if (tokens <= 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (dtype == DTYPE_F32)
-        gated_rmsnorm_kernel<float><<<tokens, threads, 0, stream>>>(o, (const float*)proj, ld, g_off,
-                                                                   gain, (float*)y, width, eps);
-    else
-        gated_rmsnorm_kernel<bf16><<<tokens, threads, 0, stream>>>(o, (const bf16*)proj, ld, g_off,
-                                                                  gain, (bf16*)y, width, eps);
-    return FSIE_LAUNCH_CHECK();
+        return launch_dependent(gated_rmsnorm_kernel<float>, tokens, threads, 0, stream, o,
+                                (const float*)proj, ld, g_off, gain, (float*)y, width, eps);
+    return launch_dependent(gated_rmsnorm_kernel<bf16>, tokens, threads, 0, stream, o,
+                            (const bf16*)proj, ld, g_off, gain, (bf16*)y, width, eps);
 }
 
 }  // extern "C"

@@ -49,6 +49,8 @@ __global__ void conv_norm_rotate_kernel(const T* __restrict__ proj, int ld, int 
                                         int vdim, int has_kv, float eps, int* error) {
     extern __shared__ float y[];                       // the convolved row, then per-head value scales
     __shared__ float scratch[32];
+    grid_dependency_wait();
+    grid_dependents_go();
     const int t = blockIdx.x;
     const int item = item_of_token(item_qstart, items, t);
     const int slot = item_slots[item];
@@ -142,6 +144,8 @@ template <typename T>
 __global__ void conv_tails_kernel(const T* __restrict__ proj, int ld, const int* __restrict__ item_qstart,
                                   const int* __restrict__ item_qlen, const int* __restrict__ item_slots,
                                   float* __restrict__ tails, int taps, int width) {
+    grid_dependency_wait();
+    grid_dependents_go();
     const int item = blockIdx.x;
     const int slot = item_slots[item];
     if (slot < 0) return;
@@ -178,12 +182,13 @@ int fsie_conv_norm_rotate(const void* proj, int ld, int tokens, int items, const
     const size_t smem = (size_t)(width + kv_heads) * sizeof(float);
     if (smem > 200 * 1024) return ERR_UNSUPPORTED;
     const int threads = width >= 1024 ? 512 : 256;
+    int code = 0;
 #define FSIE_PREPARE(T)                                                                          \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
             cudaFuncSetAttribute(conv_norm_rotate_kernel<T>,                                     \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        conv_norm_rotate_kernel<T><<<tokens, threads, smem, stream>>>(                           \
+        code = launch_dependent(conv_norm_rotate_kernel<T>, tokens, threads, smem, stream,       \
             (const T*)proj, ld, items, item_qstart, item_pos0, item_slots, tails, conv_w, taps,  \
             q_gain, k_gain, cos_sin, table_len, rot_dims, slot_of, (T*)k_pages, (T*)v_pages,     \
             page_stride, page_size, q_out, heads, kv_heads, dim, vdim, has_kv, eps, error);      \
@@ -191,7 +196,7 @@ int fsie_conv_norm_rotate(const void* proj, int ld, int tokens, int items, const
     if (dtype == DTYPE_F32) FSIE_PREPARE(float);
     else FSIE_PREPARE(bf16);
 #undef FSIE_PREPARE
-    return FSIE_LAUNCH_CHECK();
+    return code;
 }
 
 int fsie_conv_tails(const void* proj, int ld, const int* item_qstart, const int* item_qlen,
@@ -199,12 +204,10 @@ int fsie_conv_tails(const void* proj, int ld, const int* item_qstart, const int*
                     cudaStream_t stream) {
     if (items <= 0 || taps <= 1) return 0;
     if (dtype == DTYPE_F32)
-        conv_tails_kernel<float><<<items, 256, 0, stream>>>((const float*)proj, ld, item_qstart,
-                                                           item_qlen, item_slots, tails, taps, width);
-    else
-        conv_tails_kernel<bf16><<<items, 256, 0, stream>>>((const bf16*)proj, ld, item_qstart,
-                                                          item_qlen, item_slots, tails, taps, width);
-    return FSIE_LAUNCH_CHECK();
+        return launch_dependent(conv_tails_kernel<float>, items, 256, 0, stream, (const float*)proj, ld,
+                                item_qstart, item_qlen, item_slots, tails, taps, width);
+    return launch_dependent(conv_tails_kernel<bf16>, items, 256, 0, stream, (const bf16*)proj, ld,
+                            item_qstart, item_qlen, item_slots, tails, taps, width);
 }
 
 }  // extern "C"

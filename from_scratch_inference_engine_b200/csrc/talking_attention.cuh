@@ -65,6 +65,36 @@ struct TalkingLayout {
     }
 };
 
+// One tile of keys (or values) of every key/value head from the pages into shared memory
+// [g][key][ld], zero beyond `width` and for keys without a page: a warp copies a row, 16 bytes
+// per lane where the rows allow it.
+template <typename T>
+__device__ __forceinline__ void copy_tile(T* __restrict__ dst, const T* __restrict__ pages,
+                                          const int* key_page, const int* key_off, int G, int keys,
+                                          int width, int width8, int ld, long long page_stride,
+                                          int page_size, int warp, int lane) {
+    constexpr int PER = 16 / (int)sizeof(T);                 // elements of one 16-byte piece
+    const bool wide = width % PER == 0 && page_stride % PER == 0 &&
+                      (reinterpret_cast<uintptr_t>(pages) & 15) == 0;
+    for (int row = warp; row < G * keys; row += TA_WARPS) {
+        const int g = row / keys, jj = row - g * keys;
+        const int page = key_page[jj];
+        T* to = dst + (size_t)row * ld;
+        const T* from = page < 0 ? nullptr :
+            pages + page * page_stride + ((size_t)g * page_size + key_off[jj]) * width;
+        if (wide) {
+            for (int piece = lane; piece * PER < width8; piece += 32) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (from && piece * PER < width) v = *reinterpret_cast<const uint4*>(from + piece * PER);
+                *reinterpret_cast<uint4*>(to + piece * PER) = v;
+            }
+        } else {
+            for (int d = lane; d < width8; d += 32)
+                to[d] = (from && d < width) ? from[d] : from_float<T>(0.f);
+        }
+    }
+}
+
 // Warp w owns heads w, w + 8, ... (HS = 8 / TOK of them at most) and, of each, the tile's TOK
 // tokens: rows that share their keys and values, so one load of a key or value serves TOK rows.
 // Lane l owns keys l (+ 32) of a tile for the scores and value columns 2 l, 2 l + 1 (+ 64 c).
@@ -166,12 +196,8 @@ __global__ void __launch_bounds__(TA_WARPS * 32) talking_attention_kernel(const 
             }
             __syncthreads();
             // keys of every key/value head: [g][key][dim8], zero beyond dim and beyond the tile
-            for (int idx = threadIdx.x; idx < G * TK * L.dim8; idx += blockDim.x) {
-                const int d = idx % L.dim8, jj = (idx / L.dim8) % TK, g = idx / (L.dim8 * TK);
-                const int page = key_page[jj];
-                kv[((size_t)g * TK + jj) * L.kv_ld + d] = (page < 0 || d >= dim) ? from_float<T>(0.f) :
-                    k_pages[page * a.page_stride + ((size_t)g * a.page_size + key_off[jj]) * dim + d];
-            }
+            copy_tile<T>(kv, k_pages, key_page, key_off, G, TK, dim, L.dim8, L.kv_ld, a.page_stride,
+                         a.page_size, warp, lane);
             __syncthreads();
 #pragma unroll
             for (int hs = 0; hs < HS; ++hs) {
@@ -243,12 +269,8 @@ __global__ void __launch_bounds__(TA_WARPS * 32) talking_attention_kernel(const 
                 P2[idx] = m;
             }
             // values of every key/value head: [g][key][vdim8], zero beyond vdim and beyond the tile
-            for (int idx = threadIdx.x; idx < G * TK * L.vdim8; idx += blockDim.x) {
-                const int d = idx % L.vdim8, jj = (idx / L.vdim8) % TK, g = idx / (L.vdim8 * TK);
-                const int page = key_page[jj];
-                kv[((size_t)g * TK + jj) * L.kv_ld + d] = (page < 0 || d >= vdim) ? from_float<T>(0.f) :
-                    v_pages[page * a.page_stride + ((size_t)g * a.page_size + key_off[jj]) * vdim + d];
-            }
+            copy_tile<T>(kv, v_pages, key_page, key_off, G, TK, vdim, L.vdim8, L.kv_ld, a.page_stride,
+                         a.page_size, warp, lane);
             __syncthreads();
 #pragma unroll
             for (int hs = 0; hs < HS; ++hs) {

@@ -47,7 +47,7 @@ __device__ __forceinline__ void tm_split(float x, float y, unsigned& hi, unsigne
 }
 
 template <int DIM, int VDIM>
-__global__ void __launch_bounds__(256) talking_attention_mma_kernel(const TalkingMmaArgs a) {
+__global__ void __launch_bounds__(256, 2) talking_attention_mma_kernel(const TalkingMmaArgs a) {
     constexpr int QLD = DIM + 8, VLD = VDIM + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.heads, G = a.kv_heads;
@@ -75,15 +75,6 @@ __global__ void __launch_bounds__(256) talking_attention_mma_kernel(const Talkin
         Qs[r * QLD + d] = __float2bfloat16_rn(r < n_tok ? a.q[((size_t)(token0 + r) * H + h) * DIM + d] : 0.f);
     }
     __syncthreads();
-    unsigned qa[DIM / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < DIM / 16; ++ks) {
-        const bf16* base = Qs + ks * 16 + 2 * t;
-        qa[ks][0] = *reinterpret_cast<const unsigned*>(base + g * QLD);
-        qa[ks][1] = *reinterpret_cast<const unsigned*>(base + (g + 8) * QLD);
-        qa[ks][2] = *reinterpret_cast<const unsigned*>(base + g * QLD + 8);
-        qa[ks][3] = *reinterpret_cast<const unsigned*>(base + (g + 8) * QLD + 8);
-    }
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
     float acc[VDIM / 8][4];
 #pragma unroll
@@ -129,13 +120,21 @@ __global__ void __launch_bounds__(256) talking_attention_mma_kernel(const Talkin
 #pragma unroll
         for (int nt = 0; nt < TM_KEYS / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < DIM / 16; ++ks)
+        for (int ks = 0; ks < DIM / 16; ++ks) {
+            // the q fragment of this step (the tile stays in shared memory: keeping all steps'
+            // fragments in registers would halve the blocks an SM holds)
+            const bf16* base = Qs + ks * 16 + 2 * t;
+            const unsigned qa[4] = {*reinterpret_cast<const unsigned*>(base + g * QLD),
+                                    *reinterpret_cast<const unsigned*>(base + (g + 8) * QLD),
+                                    *reinterpret_cast<const unsigned*>(base + g * QLD + 8),
+                                    *reinterpret_cast<const unsigned*>(base + (g + 8) * QLD + 8)};
 #pragma unroll
             for (int nt = 0; nt < TM_KEYS / 8; ++nt) {
                 const bf16* kb = Ks + (nt * 8 + g) * QLD + ks * 16 + 2 * t;
-                tm_mma(s[nt], qa[ks], *reinterpret_cast<const unsigned*>(kb),
+                tm_mma(s[nt], qa, *reinterpret_cast<const unsigned*>(kb),
                        *reinterpret_cast<const unsigned*>(kb + 8));
             }
+        }
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < TM_KEYS / 8; ++nt)

@@ -791,7 +791,9 @@ def hybrid():
         i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
         lib.fsie_add_layernorm.argtypes = [p, p, p, p, p, i, i, f, i, i, p]
         lib.fsie_cast_rows.argtypes = [p, p, ll, i, p]
-        lib.fsie_lightning_scan.argtypes = [p, i, i, i, i, p, p, p, i, p, p, p, i, i, i, p, p, i, i, p, i, p]
+        lib.fsie_lightning_scan.argtypes = [p, i, i, i, i, p, p, p, i, p, p, p, i, i, i, p, p, i, i, p, p]
+        lib.fsie_silu_rows.argtypes = [p, i, i, p, i, i, p]
+        lib.fsie_silu_rows.restype = i
         lib.fsie_gated_rmsnorm.argtypes = [p, p, i, i, p, p, i, i, f, i, p]
         lib.fsie_conv_norm_rotate.argtypes = [p, i, i, i, p, p, p, p, p, i, p, p, p, i, i, p, p, p,
                                               ll, i, p, i, i, i, i, i, f, i, p, p]
@@ -868,21 +870,34 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def silu_rows(proj: torch.Tensor, width: int, act: torch.Tensor) -> torch.Tensor:
+    """act[t, c] = silu(proj[t, c]) for the first `width` columns, as float32 [tokens, width]."""
+    _need(proj, None, "proj")
+    _need(act, torch.float32, "act")
+    tokens, ld = proj.shape
+    if width > ld or act.numel() < tokens * width:
+        raise KernelError("silu_rows: shapes do not fit")
+    _check(hybrid().fsie_silu_rows(_ptr(proj), ld, width, _ptr(act), tokens, _tag(proj.dtype),
+                                   _stream()), "silu_rows")
+    return act
+
+
 def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
                    item_qstart: torch.Tensor, item_qlen: torch.Tensor, item_slots: torch.Tensor,
                    items: int, state: torch.Tensor, decay: torch.Tensor, out: torch.Tensor,
                    heads: int, dim: int, vdim: int, seg_item: Optional[torch.Tensor] = None,
                    seg_row0: Optional[torch.Tensor] = None, num_segs: int = 0, seg_tokens: int = 0,
                    chunk_states: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Per request and head, token by token: S = decay * S + silu(k) silu(v)^T, o = S^T silu(q).
-    proj [tokens, ld] holds the projections at the given column offsets; state [slots, heads,
-    dim, vdim] (float32) is read and left updated; out [tokens, heads * vdim] float32.
+    """Per request and head, token by token: S = decay * S + k v^T, o = S^T q.  proj [tokens, ld]
+    (float32) holds the ACTIVATED projections (`silu_rows`) at the given column offsets; state
+    [slots, heads, dim, vdim] (float32) is read and left updated; out [tokens, heads * vdim]
+    float32.
 
     With `seg_item` / `seg_row0` (int32, one entry per chunk of `seg_tokens` tokens, listed
     request by request) and `chunk_states` (float32, num_segs * heads * dim * vdim at least) the
     chunks of long prompts run side by side: each sums its own tokens, the sums are chained into
     the state at every chunk's start, and each chunk runs again from there for its outputs."""
-    _need(proj, None, "proj")
+    _need(proj, torch.float32, "proj")
     _need(state, torch.float32, "state")
     _need(decay, torch.float32, "decay")
     _need(out, torch.float32, "out")
@@ -905,7 +920,7 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
                                         _ptr(item_qlen), _ptr(item_slots), items, _ptr(state),
                                         _ptr(decay), _ptr(out), heads, dim, vdim, _ptr(seg_item),
                                         _ptr(seg_row0), num_segs, seg_tokens, _ptr(chunk_states),
-                                        _tag(proj.dtype), _stream()), "lightning_scan")
+                                        _stream()), "lightning_scan")
     return out
 
 

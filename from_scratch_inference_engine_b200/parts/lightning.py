@@ -76,7 +76,10 @@ class LightningAttention(Mixer):
                           seg_tokens=self.CHUNK_TOKENS,
                           chunk_states=ctx.scratch("lightning.chunk_states",
                                                    tiles.count * self.heads * self.dim * self.vdim))
-        ops.lightning_scan(proj, 0, self.qk_width, 2 * self.qk_width, ctx.item_qstart,
+        # the activations of q, k and v once, in 32-bit: the scan reads each of them several times
+        width = 2 * self.qk_width + self.v_width
+        act = ops.silu_rows(proj, width, rt.buffer("lightning.act", tokens, width, torch.float32))
+        ops.lightning_scan(act, 0, self.qk_width, 2 * self.qk_width, ctx.item_qstart,
                            ctx.item_qlen, ctx.item_slots, ctx.num_items, cache.state, self.decay, o,
                            self.heads, self.dim, self.vdim, **chunks)
         gated = rt.buffer("lightning.gated", tokens, self.v_width, proj.dtype)

@@ -110,6 +110,7 @@ def test_lightning_scan_carries_state_between_calls(heads, dim, vdim):
     for call in range(2):
         parts = [proj[k][sum(lengths[k][:call]):sum(lengths[k][:call + 1])] for k in ("a", "b")]
         batch = torch.cat(parts).cuda()
+        batch = ops.silu_rows(batch, width, torch.empty_like(batch))
         qlen = torch.tensor([len(p) for p in parts], dtype=torch.int32)
         qstart = torch.tensor([0, len(parts[0])], dtype=torch.int32)
         out = torch.empty(batch.shape[0], heads * vdim, device="cuda")
