@@ -171,6 +171,27 @@ def test_one_mixer_whole_prompt_and_token_by_token(tmp_path_factory, name):
     assert_rows(rows, requests, folder, F32_BOUND)
 
 
+@pytest.mark.parametrize("name", ["lightning", "hybrid"])
+def test_long_prompt_sums_chunk_by_chunk(tmp_path_factory, name):
+    """A prompt long enough that the linear attention runs its chunks side by side (sums per
+    chunk, chained, then the outputs), whole and cut in two inside a chunk, beside a short
+    request in the same step; then decoding goes on from the state the chunks left."""
+    folder = folder_of(tmp_path_factory, name)
+    requests = {"long": helpers.random_ids(vocab_of(name), 331, 3),
+                "short": helpers.random_ids(vocab_of(name), 12, 4)}
+    runner = runner_for(folder, "float32", num_pages=48)
+    steps = [{"step": 0, "end": ["short"], "entries": [
+                  {"id": "long", "tokens": requests["long"][:203], "want": [0, 63, 64, 127, 128, 202]},
+                  {"id": "short", "tokens": requests["short"], "want": [11]}]},
+             {"step": 1, "end": [], "entries": [
+                  {"id": "long", "tokens": requests["long"][203:329], "want": [0, 60, 125]}]},
+             {"step": 2, "end": [], "entries": [{"id": "long", "tokens": [requests["long"][329]], "want": [0]}]},
+             {"step": 3, "end": ["long"], "entries": [{"id": "long", "tokens": [requests["long"][330]], "want": [0]}]}]
+    rows = helpers.run_trace_in_process(runner, steps)
+    assert len(rows) == 12
+    assert_rows(rows, requests, folder, F32_BOUND)
+
+
 def test_window_edge_shows_in_the_logits(tmp_path_factory):
     """The test model's softmax is sharp enough that dropping the key at the window's far edge,
     or admitting the one beyond it, or dropping the kept first tokens, moves the logits far
