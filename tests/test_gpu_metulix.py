@@ -192,6 +192,18 @@ def test_long_prompt_sums_chunk_by_chunk(tmp_path_factory, name):
     assert_rows(rows, requests, folder, F32_BOUND)
 
 
+def test_sizes_that_fit_no_vector_in_bfloat16(tmp_path_factory):
+    """Width 36, feed-forward 50, vocabulary 61, head sizes 6 and 10: no row starts on 16 bytes.
+    The bfloat16 products and kernels take their plain forms; prompt, portions and decoding."""
+    folder = folder_of(tmp_path_factory, "odd", sharpen=False)
+    requests = {"a": helpers.random_ids(vocab_of("odd"), 45, 6), "b": helpers.random_ids(vocab_of("odd"), 19, 7)}
+    runner = runner_for(folder, "bfloat16", num_pages=8)
+    for steps in (helpers.trace_whole(requests), helpers.trace_mixed(requests, seed=1, max_live=2)):
+        rows = helpers.run_trace_in_process(runner, steps)
+        assert len(rows) == 64
+        assert_rows(rows, requests, folder, BF16_BOUND)
+
+
 def test_window_edge_shows_in_the_logits(tmp_path_factory):
     """The test model's softmax is sharp enough that dropping the key at the window's far edge,
     or admitting the one beyond it, or dropping the kept first tokens, moves the logits far
