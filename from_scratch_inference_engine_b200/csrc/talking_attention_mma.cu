@@ -5,9 +5,9 @@
 //     o_h = sum_h' talk[h, h'] a_(h', g(h))
 // so every (query head, value head) pair is an ordinary one-walk attention with a running maximum,
 // and no block has to see another head's weights.  A block takes 16 consecutive tokens of one
-// request and one query head; warp c computes the scores against the head's keys (mma.sync
-// m16n8k16, bf16 operands, float accumulators), the running softmax in 32-bit, and applies the
-// weights to the values of key/value head c.  The weights enter that product as the sum of two
+// request and one query head; its warps share the scores against the head's keys (mma.sync
+// m16n8k16, bf16 operands, float accumulators; each warp a slice of the keys) and the running
+// softmax in 32-bit, and warp c applies the weights to the values of key/value head c.  The weights enter that product as the sum of two
 // bfloat16 halves (p = hi + lo, two products), which keeps 16 bits of them.  A second kernel
 // mixes the normalised partial outputs [token][head][value head][vdim] (float) into the output.
 #include "common.cuh"
@@ -48,13 +48,16 @@ __device__ __forceinline__ void tm_split(float x, float y, unsigned& hi, unsigne
 
 template <int DIM, int VDIM>
 __global__ void __launch_bounds__(256, 2) talking_attention_mma_kernel(const TalkingMmaArgs a) {
-    constexpr int QLD = DIM + 8, VLD = VDIM + 8;
+    constexpr int QLD = DIM + 8, VLD = VDIM + 8, PLD = TM_KEYS + 8, NT = TM_KEYS / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.heads, G = a.kv_heads;
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);             // [16][QLD]
     bf16* Ks = Qs + TM_ROWS * QLD;                            // [keys][QLD]
     bf16* Vs = Ks + TM_KEYS * QLD;                            // [G][keys][VLD]
-    int* key_page = reinterpret_cast<int*>(Vs + (size_t)G * TM_KEYS * VLD);
+    bf16* Ph = Vs + (size_t)G * TM_KEYS * VLD;                // [16][PLD]: the weights' high halves
+    bf16* Pl = Ph + TM_ROWS * PLD;                            // ... and what the high halves leave
+    float* shared_max = reinterpret_cast<float*>(Pl + TM_ROWS * PLD);   // [8 warps][16 rows]
+    int* key_page = reinterpret_cast<int*>(shared_max + 8 * TM_ROWS);
     int* key_off = key_page + TM_KEYS;
 
     const int tile = blockIdx.x, h = blockIdx.y, kvh = h / (H / G);
@@ -116,9 +119,12 @@ __global__ void __launch_bounds__(256, 2) talking_attention_mma_kernel(const Tal
         }
         __syncthreads();
 
-        float s[TM_KEYS / 8][4];
+        // The scores of the tile are computed once per block: warp c takes the 8-key slices c,
+        // c + G, ...; the slices' maxima and the weights (as two bfloat16 halves) meet in shared
+        // memory, from where every warp reads all of them for its own value head.
+        float s[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < TM_KEYS / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < DIM / 16; ++ks) {
             // the q fragment of this step (the tile stays in shared memory: keeping all steps'
@@ -129,15 +135,19 @@ __global__ void __launch_bounds__(256, 2) talking_attention_mma_kernel(const Tal
                                     *reinterpret_cast<const unsigned*>(base + g * QLD + 8),
                                     *reinterpret_cast<const unsigned*>(base + (g + 8) * QLD + 8)};
 #pragma unroll
-            for (int nt = 0; nt < TM_KEYS / 8; ++nt) {
+            for (int i = 0; i < NT; ++i) {
+                const int nt = c + i * G;
+                if (nt >= NT) break;
                 const bf16* kb = Ks + (nt * 8 + g) * QLD + ks * 16 + 2 * t;
-                tm_mma(s[nt], qa, *reinterpret_cast<const unsigned*>(kb),
+                tm_mma(s[i], qa, *reinterpret_cast<const unsigned*>(kb),
                        *reinterpret_cast<const unsigned*>(kb + 8));
             }
         }
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < TM_KEYS / 8; ++nt)
+        for (int i = 0; i < NT; ++i) {
+            const int nt = c + i * G;
+            if (nt >= NT) break;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int row = e >> 1, tok = g + 8 * row, key = nt * 8 + 2 * t + (e & 1);
@@ -146,14 +156,22 @@ __global__ void __launch_bounds__(256, 2) talking_attention_mma_kernel(const Tal
                 const int p_i = p_first + tok;
                 const bool see = key < n && tok < n_tok && j <= p_i &&
                     (a.window <= 0 || p_i - j < a.window || j < a.keep_first);
-                s[nt][e] = see ? s[nt][e] * a.scale : -INFINITY;
-                tile_max[row] = fmaxf(tile_max[row], s[nt][e]);
+                s[i][e] = see ? s[i][e] * a.scale : -INFINITY;
+                tile_max[row] = fmaxf(tile_max[row], s[i][e]);
             }
+        }
 #pragma unroll
         for (int row = 0; row < 2; ++row) {
             tile_max[row] = fmaxf(tile_max[row], __shfl_xor_sync(0xffffffffu, tile_max[row], 1));
             tile_max[row] = fmaxf(tile_max[row], __shfl_xor_sync(0xffffffffu, tile_max[row], 2));
-            const float m_new = fmaxf(row_max[row], tile_max[row]);
+            if (t == 0) shared_max[c * TM_ROWS + g + 8 * row] = tile_max[row];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int row = 0; row < 2; ++row) {
+            float all = -INFINITY;
+            for (int w = 0; w < G; ++w) all = fmaxf(all, shared_max[w * TM_ROWS + g + 8 * row]);
+            const float m_new = fmaxf(row_max[row], all);
             const float alpha = m_new == -INFINITY ? 1.f : expf(row_max[row] - m_new);
             row_max[row] = m_new;
             row_sum[row] *= alpha;
@@ -164,21 +182,36 @@ __global__ void __launch_bounds__(256, 2) talking_attention_mma_kernel(const Tal
             }
         }
 #pragma unroll
-        for (int nt = 0; nt < TM_KEYS / 8; ++nt)
+        for (int i = 0; i < NT; ++i) {
+            const int nt = c + i * G;
+            if (nt >= NT) break;
+            float p[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int row = e >> 1;
-                const float p = s[nt][e] == -INFINITY ? 0.f : expf(s[nt][e] - row_max[row]);
-                s[nt][e] = p;
-                row_sum[row] += p;
+                p[e] = s[i][e] == -INFINITY ? 0.f : expf(s[i][e] - row_max[e >> 1]);
+                row_sum[e >> 1] += p[e];
             }
+            unsigned hi, low;
+            tm_split(p[0], p[1], hi, low);
+            *reinterpret_cast<unsigned*>(Ph + g * PLD + nt * 8 + 2 * t) = hi;
+            *reinterpret_cast<unsigned*>(Pl + g * PLD + nt * 8 + 2 * t) = low;
+            tm_split(p[2], p[3], hi, low);
+            *reinterpret_cast<unsigned*>(Ph + (g + 8) * PLD + nt * 8 + 2 * t) = hi;
+            *reinterpret_cast<unsigned*>(Pl + (g + 8) * PLD + nt * 8 + 2 * t) = low;
+        }
+        __syncthreads();
 #pragma unroll
         for (int ks = 0; ks < TM_KEYS / 16; ++ks) {
-            unsigned hi[4], lo2[4];
-            tm_split(s[2 * ks][0], s[2 * ks][1], hi[0], lo2[0]);
-            tm_split(s[2 * ks][2], s[2 * ks][3], hi[1], lo2[1]);
-            tm_split(s[2 * ks + 1][0], s[2 * ks + 1][1], hi[2], lo2[2]);
-            tm_split(s[2 * ks + 1][2], s[2 * ks + 1][3], hi[3], lo2[3]);
+            const bf16* ph = Ph + g * PLD + ks * 16 + 2 * t;
+            const bf16* pl = Pl + g * PLD + ks * 16 + 2 * t;
+            const unsigned hi[4] = {*reinterpret_cast<const unsigned*>(ph),
+                                    *reinterpret_cast<const unsigned*>(ph + 8 * PLD),
+                                    *reinterpret_cast<const unsigned*>(ph + 8),
+                                    *reinterpret_cast<const unsigned*>(ph + 8 * PLD + 8)};
+            const unsigned lo2[4] = {*reinterpret_cast<const unsigned*>(pl),
+                                     *reinterpret_cast<const unsigned*>(pl + 8 * PLD),
+                                     *reinterpret_cast<const unsigned*>(pl + 8),
+                                     *reinterpret_cast<const unsigned*>(pl + 8 * PLD + 8)};
             const bf16* vrow = Vs + ((size_t)c * TM_KEYS + ks * 16 + (lane & 15)) * VLD;
 #pragma unroll
             for (int nt = 0; nt < VDIM / 8; ++nt) {
@@ -189,13 +222,22 @@ __global__ void __launch_bounds__(256, 2) talking_attention_mma_kernel(const Tal
             }
         }
     }
+    // every warp has summed the weights of its own key slices: the rows' sums over all of them
+    __syncthreads();
 #pragma unroll
     for (int row = 0; row < 2; ++row) {
         row_sum[row] += __shfl_xor_sync(0xffffffffu, row_sum[row], 1);
         row_sum[row] += __shfl_xor_sync(0xffffffffu, row_sum[row], 2);
+        if (t == 0) shared_max[c * TM_ROWS + g + 8 * row] = row_sum[row];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        float total = 0.f;
+        for (int w = 0; w < G; ++w) total += shared_max[w * TM_ROWS + g + 8 * row];
         const int tok = g + 8 * row;
         if (tok >= n_tok) continue;
-        const float inv = row_sum[row] > 0.f ? 1.0f / row_sum[row] : 0.f;
+        const float inv = total > 0.f ? 1.0f / total : 0.f;
         float* dst = a.partial + (((size_t)(token0 + tok) * H + h) * G + c) * VDIM;
 #pragma unroll
         for (int nt = 0; nt < VDIM / 8; ++nt)
@@ -253,8 +295,9 @@ int fsie_talking_attention_mma(const float* q, const void* k_pages, const void* 
 #define FSIE_TM(DIM, VDIM)                                                                          \
     do {                                                                                            \
         const size_t smem = ((size_t)(TM_ROWS + TM_KEYS) * (DIM + 8) +                              \
-                             (size_t)kv_heads * TM_KEYS * (VDIM + 8)) * sizeof(bf16) +              \
-                            2 * TM_KEYS * sizeof(int);                                              \
+                             (size_t)kv_heads * TM_KEYS * (VDIM + 8) +                              \
+                             2 * (size_t)TM_ROWS * (TM_KEYS + 8)) * sizeof(bf16) +                  \
+                            8 * TM_ROWS * sizeof(float) + 2 * TM_KEYS * sizeof(int);                \
         cudaFuncSetAttribute(talking_attention_mma_kernel<DIM, VDIM>,                               \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
         talking_attention_mma_kernel<DIM, VDIM><<<grid, threads, smem, stream>>>(a);                \
