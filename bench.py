@@ -21,6 +21,9 @@ A step is one decode step of a batch of 8 requests whose contexts end at 4,096 t
             tokens/s with its HBM fraction (28 GB of weights per step) and the prefill of one
             prompt against the nominal FFMA peak
 
+`--workload hybrid` measures the Metulix hybrid design beside the Qwen2 model of equal width, heads,
+feed-forward, depth and window (prefill of one prompt, decode steps of a batch, ms per kind of kernel).
+
 Between timed steps nothing flushes L2: every step streams 15 GB of weights, far more
 than the 126 MB of L2.  `--impl reference` runs the same shape and workload through the
 unmodified reference engine (its CUDA path compiled from its own sources by
