@@ -31,26 +31,36 @@ class CacheNeed:
     """What one cache entry stores per token: kv_heads x head_dim keys and kv_heads x value_dim
     values (value_dim = 0: as wide as the keys).  window = 0 keeps every key; window = W keeps
     what a query can still see of the last W, and beside them the first `keep_first` tokens of
-    the sequence, which stay visible to every later query."""
+    the sequence, which stay visible to every later query.  values_in_keys: nothing is stored
+    beside the key rows; a reader takes its values out of them (a cache of latent rows that every
+    head reads as key and as value)."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
     keep_first: int = 0
     value_dim: int = 0
+    values_in_keys: bool = False
 
     @property
     def v_dim(self) -> int:
         return self.value_dim or self.head_dim
 
+    @property
+    def stored_value_dim(self) -> int:
+        """Columns a token's values take in a page beside its keys."""
+        return 0 if self.values_in_keys else self.v_dim
+
     def covering(self, other: "CacheNeed") -> "CacheNeed":
         """The need of an entry that `other` reads as well: the same layout, and kept is what
         either of the two can still see."""
-        if (self.kv_heads, self.head_dim, self.v_dim) != (other.kv_heads, other.head_dim, other.v_dim):
+        if (self.kv_heads, self.head_dim, self.v_dim, self.values_in_keys) != \
+                (other.kv_heads, other.head_dim, other.v_dim, other.values_in_keys):
             raise ValueError(f"cache layouts differ: {self} and {other}")
         window = 0 if self.window == 0 or other.window == 0 else max(self.window, other.window)
         keep = 0 if window == 0 else max(self.keep_first, other.keep_first)
-        return CacheNeed(self.kv_heads, self.head_dim, window, keep, self.value_dim)
+        return CacheNeed(self.kv_heads, self.head_dim, window, keep, self.value_dim,
+                         self.values_in_keys)
 
 
 @dataclass

@@ -46,6 +46,11 @@ class LayerSpec:
     feed_forward_name: str = "feed_forward."
     mixer_norm_name: str = "mixer_norm."
     feed_forward_norm_name: str = "feed_forward_norm."
+    # arrangements that norm a sublayer's output as well as its input
+    mixer_out_norm: Optional[PartSpec] = None
+    feed_forward_out_norm: Optional[PartSpec] = None
+    mixer_out_norm_name: str = "mixer_out_norm."
+    feed_forward_out_norm_name: str = "feed_forward_out_norm."
 
 
 @dataclass(frozen=True)

@@ -46,6 +46,10 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     # per-request state, and windowed attention with mixed heads behind a short convolution
     "hybrid": ("layernorm.cu", "lightning.cu", "talking_attention.cu", "talking_attention_bf16.cu",
                "talking_attention_f32.cu", "talking_attention_mma.cu"),
+    # more parts: RMS norms on both sides of a sublayer, gated activations, the minGRU recurrence,
+    # attention with a scale per head and keys and values of different widths, attention over a
+    # cache of latent rows
+    "mixers": ("sandwich_norm.cu", "mingru.cu", "scaled_attention.cu", "latent_attention.cu"),
 }
 # specialisations compiled by build_all() beside the default form of every library
 DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)],

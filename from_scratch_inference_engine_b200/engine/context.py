@@ -80,6 +80,9 @@ class StepContext:
         (all three serve captured graphs, whose shapes and launch choices must not vary)."""
         self.runtime = runtime
         self._ring, self._scratch, self.error = ring, scratch, error
+        # what one part leaves for a later part of the same step (values of the step's tokens that
+        # another layer blends with its own, for instance)
+        self.shared: Dict[str, torch.Tensor] = {}
         self.num_tokens = T = len(token_ids)
         self.num_items = I = len(q_len)
         self.h_qstart = np.asarray(q_start, dtype=np.int32)

@@ -121,11 +121,11 @@ class ModelRunner:
         self.pages: List[torch.Tensor] = []
         for group in self.cache.groups:
             need = group.need
-            if need.v_dim == need.head_dim:
+            if need.v_dim == need.head_dim and not need.values_in_keys:
                 shape = (group.num_pages, len(group.entries), 2, need.kv_heads, page_size, need.head_dim)
             else:           # values of another width than the keys: [page, entry, keys then values]
-                shape = (group.num_pages, len(group.entries),
-                         need.kv_heads * page_size * (need.head_dim + need.v_dim))
+                shape = (group.num_pages, len(group.entries),   # (no values beside latent rows)
+                         need.kv_heads * page_size * (need.head_dim + need.stored_value_dim))
             self.pages.append(torch.zeros(shape, dtype=dtype, device=device))
         self.states: List[Optional[torch.Tensor]] = []
         for need in model.state_needs():
@@ -145,7 +145,8 @@ class ModelRunner:
                 else:
                     keys = needs[entry].kv_heads * page_size * needs[entry].head_dim
                     cache.k_pages = pages[:, position, :keys]
-                    cache.v_pages = pages[:, position, keys:]
+                    cache.v_pages = (cache.k_pages if needs[entry].values_in_keys
+                                     else pages[:, position, keys:])
                 cache.page_stride = pages.stride(0)
             self.layer_caches.append(cache)
         self.error = runtime.error

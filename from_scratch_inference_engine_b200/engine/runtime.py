@@ -241,10 +241,17 @@ class Runtime:
                                         self.error)
 
     def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor,
-                      tag: Optional[str] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      tag: Optional[str] = None, bias: Optional[torch.Tensor] = None,
+                      activation: str = "silu") -> torch.Tensor:
         """silu(x @ gate.T) * (x @ up.T) for the stacked weight [gate rows; up rows]: one fused
         kernel for steps of few tokens, else the library product and the SwiGLU kernel.  With a
-        `bias` (stacked like the weight) the product adds it and the SwiGLU kernel follows."""
+        `bias` (stacked like the weight) the product adds it and the SwiGLU kernel follows.  With
+        another `activation` on the gate the stacked product is followed by the kernel of gated
+        activations."""
+        if activation != "silu":
+            both = self.linear(x, gate_up, bias, None if tag is None else tag + ".gate_up")
+            return ops.gated_act(both, self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype),
+                                 activation)
         if bias is not None:
             both = self.linear(x, gate_up, bias, None if tag is None else tag + ".gate_up")
             return ops.swiglu(both, self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype))

@@ -1097,3 +1097,216 @@ def talking_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
         tokens, heads, kv_heads, dim, vdim, window, keep_first, float(scale), _ptr(error),
         _stream()), "talking_attention_mma")
     return out
+
+
+# --------------------------------------------------- more parts: norms on both sides, minGRU,
+# ------------------------------------------------- scaled attention, attention over latent rows
+_mixers = None
+
+
+def mixers():
+    """The library of the sandwich norm, the gated activation, the minGRU recurrence, the
+    attention with a scale per head and the steps of attention over a latent cache, compiled at
+    first use."""
+    global _mixers
+    if _mixers is None:
+        lib = build.load_library("mixers")
+        i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_norm_add_norm.argtypes = [p, p, p, p, p, p, i, i, f, f, i, i, p]
+        lib.fsie_gated_act.argtypes = [p, p, ll, i, i, i, p]
+        lib.fsie_mingru_scan.argtypes = [p, i, i, p, p, p, i, p, p, i, i, p, p, p, p, i, p]
+        lib.fsie_scaled_attention_rows.argtypes = []
+        lib.fsie_scaled_attention.argtypes = [p, i, p, p, p, ll, i, i, i, i, p, i, p, p, i, p, p, p, p,
+                                              p, i, p, p, i, i, i, i, i, i, p, p]
+        lib.fsie_rotate_mix_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p,
+                                              i, p, p]
+        lib.fsie_latent_prep.argtypes = [p, i, p, p, i, p, p, ll, i, p, f, p, i, i, i, i, i, i, i, p, p]
+        lib.fsie_head_product.argtypes = [p, ll, i, p, p, ll, i, i, i, i, i, i, p]
+        for name in ("fsie_norm_add_norm", "fsie_gated_act", "fsie_mingru_scan",
+                     "fsie_scaled_attention_rows", "fsie_scaled_attention", "fsie_rotate_mix_write",
+                     "fsie_latent_prep", "fsie_head_product"):
+            getattr(lib, name).restype = i
+        _mixers = lib
+    return _mixers
+
+
+def norm_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], delta_gain: Optional[torch.Tensor],
+                  delta_eps: float, gain: Optional[torch.Tensor], eps: float,
+                  out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                  write_x: bool = True) -> Optional[torch.Tensor]:
+    """x (float32 residual) += rms(delta) * delta_gain; out = rms(x) * gain in out's dtype, where
+    rms(v) = v / sqrt(mean(v^2) + eps).  Without `delta` a plain norm of x, without `out` the
+    sum alone.  With `rows` (int32 indices) only those rows, into out[0..len(rows)), and x is
+    left untouched unless write_x."""
+    _need(x, torch.float32, "x")
+    hidden = x.shape[-1]
+    dtype = out.dtype if out is not None else delta.dtype
+    if delta is not None:
+        _need(delta, dtype, "delta")
+        _need(delta_gain, torch.float32, "delta_gain")
+        if delta.shape[-1] != hidden or delta_gain.numel() != hidden:
+            raise KernelError("norm_add_norm: delta or its gain is not as wide as x")
+    if out is not None:
+        _need(out, None, "out")
+        _need(gain, torch.float32, "gain")
+        if gain.numel() != hidden:
+            raise KernelError("norm_add_norm: gain width differs from x")
+    if delta is None and out is None:
+        raise KernelError("norm_add_norm: nothing to do")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        count = rows.numel()
+    else:
+        count = x.numel() // hidden
+    if out is not None and out.numel() < count * hidden:
+        raise KernelError("norm_add_norm: out is too small")
+    _check(mixers().fsie_norm_add_norm(_ptr(x), _ptr(delta), _ptr(delta_gain), _ptr(gain), _ptr(out),
+                                       _ptr(rows), count, hidden, float(delta_eps), float(eps),
+                                       int(write_x), _tag(dtype), _stream()), "norm_add_norm")
+    return out
+
+
+GATE_KINDS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out[t, i] = f(gate_up[t, i]) * gate_up[t, inter + i] with f = SiLU or the tanh form of GELU."""
+    _need(gate_up, None, "gate_up")
+    _need(out, gate_up.dtype, "out")
+    tokens, two_inter = gate_up.shape
+    inter = two_inter // 2
+    if two_inter != 2 * inter or out.numel() < tokens * inter:
+        raise KernelError("gated_act: shapes do not fit")
+    _check(mixers().fsie_gated_act(_ptr(gate_up), _ptr(out), tokens, inter, GATE_KINDS[kind],
+                                   _tag(out.dtype), _stream()), "gated_act")
+    return out
+
+
+def mingru_scan(proj: torch.Tensor, width: int, item_qstart: torch.Tensor, item_qlen: torch.Tensor,
+                item_slots: torch.Tensor, items: int, state: torch.Tensor, out: torch.Tensor,
+                seg_item: Optional[torch.Tensor] = None, seg_row0: Optional[torch.Tensor] = None,
+                num_segs: int = 0, seg_tokens: int = 0, seg_ab: Optional[torch.Tensor] = None,
+                seg_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """proj [tokens, 3 width] = gate | candidate | output gate (biases added).  Per request and
+    channel: z = sigmoid(gate); cand = u + 1/2 (u >= 0) or sigmoid(u); S = (1 - z) S + z cand from
+    the state in the request's slot (float32 [slots, width], updated); out[t] = S_t * silu(output
+    gate).  With segments (num_segs > 0) a request's tokens run chunk-parallel."""
+    _need(proj, None, "proj")
+    _need(state, torch.float32, "state")
+    _need(out, proj.dtype, "out")
+    tokens, ld = proj.shape
+    if ld < 3 * width or out.numel() < tokens * width or state.shape[-1] != width:
+        raise KernelError("mingru_scan: shapes do not fit")
+    if num_segs:
+        if seg_ab.numel() < 2 * num_segs * width or seg_start.numel() < num_segs * width:
+            raise KernelError("mingru_scan: segment scratch is too small")
+    _check(mixers().fsie_mingru_scan(_ptr(proj), ld, width, _ptr(item_qstart), _ptr(item_qlen),
+                                     _ptr(item_slots), items, _ptr(seg_item), _ptr(seg_row0), num_segs,
+                                     seg_tokens, _ptr(state), _ptr(seg_ab), _ptr(seg_start), _ptr(out),
+                                     _tag(proj.dtype), _stream()), "mingru_scan")
+    return out
+
+
+def scaled_attention_rows() -> int:
+    return int(mixers().fsie_scaled_attention_rows())
+
+
+def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pages: torch.Tensor,
+                     v_pages: Optional[torch.Tensor], page_stride: int, page_size: int, key_dim: int,
+                     value_dim: int, values_in_keys: bool, block_tables: torch.Tensor,
+                     tile_item: torch.Tensor, tile_row0: torch.Tensor, tiles: int,
+                     item_qstart: torch.Tensor, item_qlen: torch.Tensor, item_pos0: torch.Tensor,
+                     item_slots: Optional[torch.Tensor], out: torch.Tensor, tokens: int, heads: int,
+                     kv_heads: int, window: int, error: torch.Tensor, nsplit: int = 1,
+                     part_o: Optional[torch.Tensor] = None,
+                     part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal (optionally windowed) softmax attention of q [tokens, heads x key_dim] over paged keys
+    [kv_head][slot][key_dim] and values [kv_head][slot][value_dim] (or, values_in_keys, the first
+    value_dim columns of the key rows), scores multiplied by head_scale[head]; 32-bit arithmetic."""
+    _need(q, None, "q", contiguous=False)
+    _need(head_scale, torch.float32, "head_scale")
+    _need(out, q.dtype, "out")
+    if k_pages.dtype is not q.dtype:
+        raise KernelError("scaled_attention: cache dtype differs from q")
+    if head_scale.numel() != heads or out.numel() < tokens * heads * value_dim:
+        raise KernelError("scaled_attention: shapes do not fit")
+    if nsplit > 1:
+        if part_o.numel() < nsplit * tokens * heads * value_dim or \
+                part_ml.numel() < nsplit * tokens * heads * 2:
+            raise KernelError("scaled_attention: scratch for the key splits is too small")
+    _check(mixers().fsie_scaled_attention(
+        _ptr(q), q_ld, _ptr(head_scale), _ptr(k_pages), _ptr(v_pages), page_stride, page_size, key_dim,
+        value_dim, int(values_in_keys), _ptr(block_tables), block_tables.stride(0), _ptr(tile_item),
+        _ptr(tile_row0), tiles, _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots),
+        _ptr(out), heads * value_dim, _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, window,
+        nsplit, _tag(q.dtype), _ptr(error), _stream()), "scaled_attention")
+    return out
+
+
+def rotate_mix_write(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                     slot_of: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     page_stride: int, page_size: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                     rotary_dim: int, mix_mode: int, mix: Optional[torch.Tensor],
+                     v_first: Optional[torch.Tensor], error: torch.Tensor) -> None:
+    """proj [tokens, q | k | v]: rotate q in place and k into its page over the first rotary_dim of
+    each head (pairs i, i + rotary_dim / 2); values into their page, blended with v_first
+    (mix_mode 2: v <- (1 - mix) v + mix v_first) or copied to it first (mix_mode 1)."""
+    _need(proj, None, "proj")
+    _need(positions, torch.int32, "positions")
+    _need(cos_sin, torch.float32, "cos_sin")
+    _need(slot_of, torch.int32, "slot_of")
+    tokens, ld = proj.shape
+    if rotary_dim > 0 and cos_sin.shape[-1] != rotary_dim:
+        raise KernelError("rotate_mix_write: cos/sin table width differs from rotary_dim")
+    if k_pages.dtype is not proj.dtype or v_pages.dtype is not proj.dtype:
+        raise KernelError("rotate_mix_write: cache dtype differs from the projection dtype")
+    if mix_mode:
+        _need(v_first, proj.dtype, "v_first")
+        if v_first.numel() < tokens * kv_heads * vdim:
+            raise KernelError("rotate_mix_write: v_first is too small")
+    if mix_mode == 2:
+        _need(mix, torch.float32, "mix")
+    _check(mixers().fsie_rotate_mix_write(_ptr(proj), ld, _ptr(positions), _ptr(cos_sin),
+                                          cos_sin.shape[0], _ptr(slot_of), _ptr(k_pages), _ptr(v_pages),
+                                          page_stride, page_size, tokens, heads, kv_heads, dim, vdim,
+                                          rotary_dim, mix_mode, _ptr(mix), _ptr(v_first),
+                                          _tag(proj.dtype), _ptr(error), _stream()), "rotate_mix_write")
+
+
+def latent_prep(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                slot_of: torch.Tensor, pages: torch.Tensor, page_stride: int, page_size: int,
+                gain: torch.Tensor, eps: float, qa: torch.Tensor, heads: int, dim: int, rope: int,
+                rank: int, rotary_dim: int, error: torch.Tensor) -> None:
+    """proj [tokens, heads x (dim | rope) | rank | rope]: the RMS-normed latent (gain, eps) and the
+    rotated shared key part into the token's cache row [rank | rope]; every head's rotated rope
+    part of q into qa [tokens, heads, rank + rope] behind the rank columns.  Rotation of pairs
+    (2i, 2i + 1) of the first rotary_dim columns of a rope part."""
+    _need(proj, None, "proj")
+    _need(positions, torch.int32, "positions")
+    _need(cos_sin, torch.float32, "cos_sin")
+    _need(slot_of, torch.int32, "slot_of")
+    _need(gain, torch.float32, "gain")
+    _need(qa, proj.dtype, "qa")
+    tokens, ld = proj.shape
+    if rotary_dim > 0 and cos_sin.shape[-1] != rotary_dim:
+        raise KernelError("latent_prep: cos/sin table width differs from rotary_dim")
+    if pages.dtype is not proj.dtype or gain.numel() != rank or \
+            qa.numel() < tokens * heads * (rank + rope):
+        raise KernelError("latent_prep: shapes or dtypes do not fit")
+    _check(mixers().fsie_latent_prep(_ptr(proj), ld, _ptr(positions), _ptr(cos_sin), cos_sin.shape[0],
+                                     _ptr(slot_of), _ptr(pages), page_stride, page_size, _ptr(gain),
+                                     float(eps), _ptr(qa), tokens, heads, dim, rope, rank, rotary_dim,
+                                     _tag(proj.dtype), _ptr(error), _stream()), "latent_prep")
+
+
+def head_product(x: torch.Tensor, x_ld: int, x_head: int, weight: torch.Tensor, out: torch.Tensor,
+                 out_ld: int, out_head: int, tokens: int) -> torch.Tensor:
+    """out[t, h, :] = weight[h] @ x[t, h, :] for weight [heads, n, k]; head h of token t of x at
+    t * x_ld + h * x_head, of out at t * out_ld + h * out_head.  32-bit sums."""
+    _need(x, None, "x", contiguous=False)
+    _need(weight, x.dtype, "weight")
+    _need(out, x.dtype, "out", contiguous=False)
+    heads, n, k = weight.shape
+    _check(mixers().fsie_head_product(_ptr(x), x_ld, x_head, _ptr(weight), _ptr(out), out_ld, out_head,
+                                      tokens, heads, n, k, _tag(x.dtype), _stream()), "head_product")
+    return out

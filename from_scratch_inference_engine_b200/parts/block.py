@@ -10,7 +10,7 @@ from ..config.spec import LayerSpec
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import LayerCache, Part, build_part, register_part
-from .norm import LayerNorm, RMSNorm
+from .norm import LayerNorm, NormedDelta, RMSNorm
 
 
 @register_part("arrangement", "prenorm")
@@ -130,3 +130,63 @@ class OutNormBlock(Part):
             self.feed_forward_norm.accumulate(x, out, copy)
         ctx.residual_copy = copy
         return None
+
+
+@register_part("arrangement", "sandwich")
+class SandwichBlock(Part):
+    """x += norm_b(mixer(norm_a(x))); x += norm_d(feed_forward(norm_c(x))): an RMS norm before AND
+    after each sublayer.  A layer may have no feed-forward.
+
+    The residual stream `x` is float32 and is updated in place.  A sublayer's output is not normed
+    and added at once: it is handed on with its norm's gain (`NormedDelta`), and the kernel of the
+    norm that runs next - the next sublayer's input norm, or the model's final norm - norms it,
+    adds it to x and norms the sum in one pass over the row.
+    """
+
+    def __init__(self, prefix: str, layer: LayerSpec):
+        self.prefix = prefix
+        if layer.mixer_out_norm is None or \
+                (layer.feed_forward is not None and layer.feed_forward_out_norm is None):
+            raise ValueError("the sandwich arrangement needs a norm for every sublayer's output")
+        self.mixer_norm = build_part("norm", layer.mixer_norm, prefix + layer.mixer_norm_name)
+        self.mixer = build_part("mixer", layer.mixer, prefix + layer.mixer_name)
+        self.mixer_out_norm = build_part("norm", layer.mixer_out_norm,
+                                         prefix + layer.mixer_out_norm_name)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_out_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm,
+                                                prefix + layer.feed_forward_norm_name)
+            self.feed_forward = build_part("feed_forward", layer.feed_forward,
+                                           prefix + layer.feed_forward_name)
+            self.feed_forward_out_norm = build_part("norm", layer.feed_forward_out_norm,
+                                                    prefix + layer.feed_forward_out_norm_name)
+        for norm in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm,
+                     self.feed_forward_out_norm):
+            if norm is not None and not isinstance(norm, RMSNorm):
+                raise TypeError("the sandwich arrangement takes RMS norms")
+
+    def parts(self):
+        return [part for part in (self.mixer_norm, self.mixer, self.mixer_out_norm,
+                                  self.feed_forward_norm, self.feed_forward,
+                                  self.feed_forward_out_norm) if part is not None]
+
+    @property
+    def capturable(self) -> bool:
+        return all(part.capturable for part in self.parts())
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [spec for part in self.parts() for spec in part.tensor_specs()]
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def forward(self, ctx, x: torch.Tensor, delta, cache: LayerCache) -> NormedDelta:
+        ctx.residual_copy = None
+        y = self.mixer_norm.forward(x, delta, tag="sandwich.mixer_in")
+        mixed = self.mixer_out_norm.pending(self.mixer.forward(ctx, y, cache))
+        if self.feed_forward is None:
+            return mixed
+        y = self.feed_forward_norm.forward(x, mixed, tag="sandwich.feed_forward_in")
+        return self.feed_forward_out_norm.pending(self.feed_forward.forward(ctx, y))

@@ -1,4 +1,4 @@
-"""Dense SwiGLU feed-forward."""
+"""Dense gated feed-forward (SwiGLU, or another activation on the gate)."""
 
 from __future__ import annotations
 
@@ -11,9 +11,11 @@ from ..weights.tensor_spec import TensorSpec
 from .base import Part, register_part
 
 
+@register_part("feed_forward", "gated_mlp")
 @register_part("feed_forward", "swiglu")
 class SwiGluMlp(Part):
-    """down( silu(gate(y)) * up(y) ), without biases (reference: src/model/model.cpp:136-140,
+    """down( act(gate(y)) * up(y) ) with act = SiLU unless `activation` names another
+    ("gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), without biases (reference: src/model/model.cpp:136-140,
     src/model/nn.cpp:74-88) or, with `bias`, with one on each of the three projections.  gate
     and up are one product over the stacked weight [2 * intermediate, hidden]: gate rows first,
     then up rows.  `names` gives the tensor names below the prefix: the three projections, and
@@ -25,7 +27,11 @@ class SwiGluMlp(Part):
              "bias": ".bias"}
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, bias: bool = False,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, activation: str = "silu"):
+        if activation not in ops.GATE_KINDS:
+            raise ValueError(f"unknown gate activation '{activation}' "
+                             f"({', '.join(sorted(ops.GATE_KINDS))})")
+        self.activation = activation
         self.prefix, self.hidden_size = prefix, int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         self.bias = bool(bias)
@@ -58,11 +64,12 @@ class SwiGluMlp(Part):
             self.b_down = tensors[self._name("down", "bias")].to(runtime.dtype).contiguous()
         # the fused SwiGLU products take no bias: with one, the stacked product adds it and a
         # kernel of its own applies the activation
-        runtime.prepare_weight(self.w_gate_up, swiglu=not self.bias)
+        runtime.prepare_weight(self.w_gate_up, swiglu=not self.bias and self.activation == "silu")
         runtime.prepare_weight(self.w_down)
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         rt = self.runtime
         # the activation and the result are dead when the next feed-forward of the model runs
-        act = rt.linear_swiglu(y, self.w_gate_up, "swiglu.act", bias=self.b_gate_up)
+        act = rt.linear_swiglu(y, self.w_gate_up, "swiglu.act", bias=self.b_gate_up,
+                               activation=self.activation)
         return rt.linear(act, self.w_down, self.b_down, "swiglu.down")

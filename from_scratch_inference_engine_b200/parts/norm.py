@@ -2,13 +2,25 @@
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Union
 
 import torch
 
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import Part, register_part
+
+
+@dataclass
+class NormedDelta:
+    """A sublayer's output that is still to be RMS-normed (gain, eps) and added to the residual
+    stream: what an arrangement with norms on the sublayers' outputs hands to the norm that runs
+    next, so that one kernel norms it, adds it and norms the sum."""
+
+    delta: torch.Tensor
+    gain: torch.Tensor          # float32 [width]
+    eps: float
 
 
 @register_part("norm", "rmsnorm")
@@ -21,24 +33,42 @@ class RMSNorm(Part):
 
     capturable = True
 
-    def __init__(self, prefix: str, width: int, eps: float):
+    def __init__(self, prefix: str, width: int, eps: float, weight_name: str = "weight"):
         self.prefix, self.width, self.eps = prefix, int(width), float(eps)
+        self.name = prefix + weight_name
         self.gain: Optional[torch.Tensor] = None
+        self._gain_f32: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.prefix + "weight", (self.width,), role="vector", init="gain")]
+        return [TensorSpec(self.name, (self.width,), role="vector", init="gain")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
         self.runtime = runtime
-        self.gain = tensors[self.prefix + "weight"].contiguous()
+        self.gain = tensors[self.name].contiguous()
+        self._gain_f32 = None
 
-    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor],
+    @property
+    def gain_f32(self) -> torch.Tensor:
+        """The gain in 32-bit (what the kernels that norm on both sides of a sublayer read)."""
+        if self._gain_f32 is None:
+            self._gain_f32 = self.gain.to(torch.float32).contiguous()
+        return self._gain_f32
+
+    def forward(self, x: torch.Tensor, delta: Union[None, torch.Tensor, NormedDelta],
                 rows: Optional[torch.Tensor] = None, write_x: bool = True,
                 tag: Optional[str] = None) -> torch.Tensor:
-        """`tag`: where the result may live (`Runtime.buffer`); None asks for fresh memory."""
+        """`tag`: where the result may live (`Runtime.buffer`); None asks for fresh memory.
+        `delta` is added to x as it is, or - a `NormedDelta` - after its own RMS norm."""
         count = x.shape[0] if rows is None else rows.numel()
         out = self.runtime.buffer(tag, count, self.width, self.runtime.dtype)
+        if isinstance(delta, NormedDelta):
+            return ops.norm_add_norm(x, delta.delta, delta.gain, delta.eps, self.gain_f32, self.eps,
+                                     out, rows=rows, write_x=write_x)
         return ops.add_rmsnorm(x, delta, self.gain, self.eps, out, rows=rows, write_x=write_x)
+
+    def pending(self, delta: torch.Tensor) -> NormedDelta:
+        """`delta`, to be normed by this norm and added by whichever norm runs next."""
+        return NormedDelta(delta, self.gain_f32, self.eps)
 
 
 @register_part("norm", "layernorm")

@@ -58,6 +58,8 @@ def random_tensor(spec: TensorSpec, seed: int, std: float, dtype: torch.dtype) -
         values = std * standard_normal(seed, spec.name, count)
     elif spec.init == "taps":
         values = 0.5 * standard_normal(seed, spec.name, count)
+    elif spec.init == "half":
+        values = 0.5 + std * standard_normal(seed, spec.name, count)
     elif spec.init == "eye":
         values = np.eye(*spec.shape).reshape(-1) + std * standard_normal(seed, spec.name, count)
     else:
@@ -92,11 +94,13 @@ def random_tensors_on_device(specs: Iterable[TensorSpec], seed: int, std: float 
             raise ValueError(f"no random recipe for integer table {spec.name}")
         if spec.init in ("zeros", "ones"):
             values = torch.full(spec.shape, float(spec.init == "ones"), device=device)
-        elif spec.init in ("gain", "normal", "taps", "eye"):
+        elif spec.init in ("gain", "normal", "taps", "eye", "half"):
             values = torch.randn(spec.shape, generator=generator, device=device,
                                  dtype=torch.float32) * (0.5 if spec.init == "taps" else std)
             if spec.init == "gain":
                 values += 1.0
+            elif spec.init == "half":
+                values += 0.5
             elif spec.init == "eye":
                 values += torch.eye(*spec.shape, device=device)
         else:

@@ -15,7 +15,8 @@ class TensorSpec:
               "table":  integer table, held as int32.
     init      how the random-weights mode draws it: "normal" (N(0, std)),
               "gain" (1 + N(0, std)), "zeros", "ones", "taps" (N(0, 0.5): the taps of a short
-              convolution, whose scale a norm behind it removes) or "eye" (identity + N(0, std):
+              convolution, whose scale a norm behind it removes), "half" (1/2 + N(0, std): a blending
+              weight) or "eye" (identity + N(0, std):
               a matrix that mixes heads).
     optional  may be absent from the checkpoint (the part says what it does then).
     same_as   when present in the checkpoint it must equal this other tensor
