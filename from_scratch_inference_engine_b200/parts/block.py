@@ -164,6 +164,12 @@ class SandwichBlock(Part):
                      self.feed_forward_out_norm):
             if norm is not None and not isinstance(norm, RMSNorm):
                 raise TypeError("the sandwich arrangement takes RMS norms")
+        # a checkpoint may still hold the norms of a feed-forward that the layer does not have
+        self.unused = []
+        if layer.feed_forward is None:
+            width = self.mixer_norm.width
+            self.unused = [TensorSpec(prefix + name, (width,), role="vector", init="gain", optional=True)
+                           for name in (layer.feed_forward_norm_name, layer.feed_forward_out_norm_name)]
 
     def parts(self):
         return [part for part in (self.mixer_norm, self.mixer, self.mixer_out_norm,
@@ -175,7 +181,7 @@ class SandwichBlock(Part):
         return all(part.capturable for part in self.parts())
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [spec for part in self.parts() for spec in part.tensor_specs()]
+        return [spec for part in self.parts() for spec in part.tensor_specs()] + self.unused
 
     def bind(self, tensors, runtime) -> None:
         self.runtime = runtime

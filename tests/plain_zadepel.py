@@ -119,6 +119,33 @@ def masked_softmax(scores, visible):
     return torch.softmax(scores, dim=-1)
 
 
+def windowed_attention(q, k, v, head_scale, q_pos, k_pos, window=0):
+    """q [n, heads, dk], k [m, groups, dk], v [m, groups, dv]; query at position p sees the keys at
+    positions j with 0 <= p - j (< window, if one is given); head h reads group h // (heads / groups);
+    scores times head_scale[h]."""
+    heads, groups = q.shape[1], k.shape[1]
+    kk = k.repeat_interleave(heads // groups, dim=1)
+    vv = v.repeat_interleave(heads // groups, dim=1)
+    scores = torch.einsum("ihd,jhd->hij", q, kk) * torch.as_tensor(head_scale, dtype=F64).reshape(-1, 1, 1)
+    gap = torch.as_tensor(q_pos)[:, None] - torch.as_tensor(k_pos)[None, :]
+    visible = gap >= 0
+    if window:
+        visible = visible & (gap < window)
+    return torch.einsum("hij,jhd->ihd", masked_softmax(scores, visible), vv)
+
+
+def mingru_states(a, u, start=None):
+    """a, u [tokens, width]: the states after every token, from `start` (zeros)."""
+    z = torch.sigmoid(a)
+    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    state = torch.zeros(a.shape[1], dtype=F64) if start is None else start.to(F64)
+    states = []
+    for p in range(a.shape[0]):
+        state = (1.0 - z[p]) * state + z[p] * cand[p]
+        states.append(state)
+    return torch.stack(states)
+
+
 def latent_attention(h, t, prefix, m, eps, positions):
     heads, dim, rot_dim, vdim, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     n = h.shape[0]
@@ -132,16 +159,12 @@ def latent_attention(h, t, prefix, m, eps, positions):
     k_rope = rotate_interleaved(k_rope, positions, base, dims)
     k_nope = (c @ t[prefix + "uk"].T).reshape(n, heads, dim)
     v = (c @ t[prefix + "uv"].T).reshape(n, heads, vdim)
-    scores = (torch.einsum("ihd,jhd->hij", q_nope, k_nope)
-              + torch.einsum("ihd,jd->hij", q_rope, k_rope)) * m["scale"]
-    gap = positions[:, None] - positions[None, :]
-    visible = gap >= 0
+    # every head's keys are its own unrotated part and the shared rotated part side by side
+    q_full = torch.cat([q_nope, q_rope], dim=-1)
+    k_full = torch.cat([k_nope, k_rope[:, None, :].expand(n, heads, rot_dim)], dim=-1)
     size = (m.get("mask") or {}).get("size", 0)
-    if size:
-        visible = visible & (gap < size)
-    w = masked_softmax(scores, visible)
-    o = torch.einsum("hij,jhd->ihd", w, v).reshape(n, heads * vdim)
-    return o @ t[prefix + "o"].T
+    o = windowed_attention(q_full, k_full, v, [m["scale"]] * heads, positions, positions, size)
+    return o.reshape(n, heads * vdim) @ t[prefix + "o"].T
 
 
 def attention(h, t, prefix, m, positions, shared):
@@ -160,26 +183,12 @@ def attention(h, t, prefix, m, positions, shared):
             v = (1.0 - lam) * v + lam * shared["v_first"]
         else:
             shared["v_first"] = v
-    group = heads // kv_heads
-    kk = k.repeat_interleave(group, dim=1)
-    vv = v.repeat_interleave(group, dim=1)
-    scores = torch.einsum("ihd,jhd->hij", q, kk) * m["scale"] * t[prefix + "temp"][:, None, None]
-    gap = positions[:, None] - positions[None, :]
-    w = masked_softmax(scores, gap >= 0)
-    o = torch.einsum("hij,jhd->ihd", w, vv).reshape(n, heads * vdim)
-    return o @ t[prefix + "o"].T
+    o = windowed_attention(q, k, v, m["scale"] * t[prefix + "temp"], positions, positions)
+    return o.reshape(n, heads * vdim) @ t[prefix + "o"].T
 
 
 def mingru(h, t, prefix):
-    z = torch.sigmoid(h @ t[prefix + "z"].T + t[prefix + "z.b"])
-    u = h @ t[prefix + "x"].T + t[prefix + "x.b"]
-    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
-    state = torch.zeros(z.shape[1], dtype=F64)
-    states = []
-    for p in range(h.shape[0]):
-        state = (1.0 - z[p]) * state + z[p] * cand[p]
-        states.append(state)
-    s = torch.stack(states)
+    s = mingru_states(h @ t[prefix + "z"].T + t[prefix + "z.b"], h @ t[prefix + "x"].T + t[prefix + "x.b"])
     return (s * silu(h @ t[prefix + "g"].T)) @ t[prefix + "o"].T
 
 
@@ -215,6 +224,11 @@ def forward(config, t, tokens, return_layers=False):
         after.append(x)
     logits = rms_norm(x, t["final.norm"], eps) @ t["embed"].T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def logits_of(model_dir, tokens):
+    config, t = load(model_dir)
+    return forward(config, t, tokens)
 
 
 def greedy(config, t, prompt, new_tokens):
