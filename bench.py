@@ -22,7 +22,9 @@ A step is one decode step of a batch of 8 requests whose contexts end at 4,096 t
             prompt against the nominal FFMA peak
 
 `--workload hybrid` measures the Metulix hybrid design beside the Qwen2 model of equal width, heads,
-feed-forward, depth and window (prefill of one prompt, decode steps of a batch, ms per kind of kernel).
+feed-forward, depth and window (prefill of one prompt, decode steps of a batch, ms per kind of kernel);
+`--workload zadepel` does the same for the Zadepel design (latent attention, grouped-query attention with
+blended values, minGRU) beside Qwen2 with full causal attention.
 
 Between timed steps nothing flushes L2: every step streams 15 GB of weights, far more
 than the 126 MB of L2.  `--impl reference` runs the same shape and workload through the
@@ -416,8 +418,33 @@ def hybrid_shapes(width, heads, kv_heads, dim, ff, layers, vocab, window, keep_f
     return metulix, qwen
 
 
-def hybrid_workload(args) -> int:
-    """The Metulix design beside the Qwen2 model of equal size (random bf16 weights): prefill of
+def zadepel_shapes(width, heads, kv_heads, dim, ff, layers, vocab, window, keep_first):
+    """A Zadepel model (latent attention under a window, grouped-query attention with blended
+    values, minGRU, grouped-query attention again, repeated; every layer with a GELU-gated
+    feed-forward) and the Qwen2 model of equal width, heads, head size, feed-forward, depth and
+    vocabulary with full causal attention."""
+    mlp = {"kind": "dense", "ff": ff}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": 4 * dim,
+        "scale": (dim + dim // 2) ** -0.5, "rot": {"base": 10000.0, "dims": dim // 2},
+        "mask": {"size": window}}}
+    attention = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+        "rot": {"base": 250000.0, "dims": dim // 2}, "v_mix": True}}
+    mingru = {"type": "mingru", "mlp": mlp, "mixer": {"width": 2 * width}}
+    order = (latent, attention, mingru, attention)
+    zadepel = {"architecture": "Zadepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+               "layers": [order[i % 4] for i in range(layers)]}
+    qwen = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=layers,
+                hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=dim,
+                intermediate_size=ff, vocab_size=vocab, rope_theta=10000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=True, max_position_embeddings=8192, use_sliding_window=False)
+    return zadepel, qwen
+
+
+def hybrid_workload(args, design="metulix") -> int:
+    """The Metulix design (or, `design`, the Zadepel design) beside the Qwen2 model of equal size
+    (random bf16 weights): prefill of
     one prompt and decode steps of a batch, through the same step function, timed on the device
     with CUDA events; and where the time goes, per kind of kernel, from events around every
     launch of one prefill step and one decode step (run without graphs for that).  One JSON line."""
@@ -448,7 +475,8 @@ def hybrid_workload(args) -> int:
                                "gemm_decode", "gemm_skinny", "gemm_skinny_qkv_rope", "gemm_tiles",
                                "layernorm_rows", "add_layernorm", "cast_rows", "silu_rows", "lightning_scan",
                                "gated_rmsnorm", "conv_norm_rotate", "conv_tails", "talking_attention",
-                               "talking_attention_mma")
+                               "talking_attention_mma", "norm_add_norm", "gated_act", "mingru_scan",
+                               "scaled_attention", "rotate_mix_write", "latent_prep", "head_product")
              if hasattr(ops, name)]
 
     def by_kind(fn):
@@ -490,10 +518,11 @@ def hybrid_workload(args) -> int:
     clocks.start()
     for name, width, heads, kv_heads, dim, ff, layers, vocab in sizes:
         layers = args.layers or layers
-        shapes = hybrid_shapes(width, heads, kv_heads, dim, ff, layers, vocab, window, keep_first)
+        shapes = (zadepel_shapes if design == "zadepel" else hybrid_shapes)(
+            width, heads, kv_heads, dim, ff, layers, vocab, window, keep_first)
         entry = {"size": name, "width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
                  "ff": ff, "layers": layers, "vocab": vocab, "window": window, "keep_first": keep_first}
-        for design, shape in zip(("metulix", "qwen2"), shapes):
+        for name_of_design, shape in zip((design, "qwen2"), shapes):
             config = config_from_dict(shape)
             model = LoadedModel.from_random(config, seed=0, std=0.02, dtype=compute,
                                             max_positions=max(context, prompt_len) + 64)
@@ -553,13 +582,13 @@ def hybrid_workload(args) -> int:
                 runner.raise_on_device_error()
                 del runner
                 torch.cuda.empty_cache()
-            entry[design] = results_design
+            entry[name_of_design] = results_design
             del model
             torch.cuda.empty_cache()
         results.append(entry)
     clock_record = clocks.stop()
     print(json.dumps({
-        "metric": "prefill and decode tokens/s of the Metulix design beside Qwen2 at equal size",
+        "metric": f"prefill and decode tokens/s of the {design.capitalize()} design beside Qwen2 at equal size",
         "impl": "engine", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "dtype": "bf16" if compute == "bfloat16" else "fp32",
         "config": {"prefill_tokens": prompt_len, "decode_batch": batch, "decode_context": context,
@@ -649,12 +678,13 @@ def main() -> int:
                              "blocks it falls to instead of sharing it out among all (for measuring that choice)")
     parser.add_argument("--fp32-steps", type=int, default=8,
                         help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline", "hybrid"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline", "hybrid", "zadepel"],
                         help="decode: the default measurement; serving: continuous batching of 256 "
                              "requests at the 1.5B shape; long: the 14B shape, decode at batch 32 with "
                              "8,192-token contexts and chunked prefill of an 8,192-token prompt; "
                              "timeline: kernel start and end times inside one decode step (text); "
-                             "hybrid: the Metulix design beside Qwen2 at equal sizes, prefill and decode")
+                             "hybrid: the Metulix design beside Qwen2 at equal sizes, prefill and decode; "
+                             "zadepel: the same for the Zadepel design")
     parser.add_argument("--sizes", default="", help="hybrid: which sizes to run (w2048,w4096; '' = all)")
     parser.add_argument("--requests", type=int, default=256)
     parser.add_argument("--step-tokens", type=int, default=2048, help="serving: token budget of one step")
@@ -678,6 +708,8 @@ def main() -> int:
         return timeline_workload(args)
     if args.workload == "hybrid":
         return hybrid_workload(args)
+    if args.workload == "zadepel":
+        return hybrid_workload(args, design="zadepel")
 
     import numpy as np
     import torch

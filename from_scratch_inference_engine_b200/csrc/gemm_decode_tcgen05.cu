@@ -39,6 +39,7 @@ struct GemmParams {
     const bf16* bias;               // [N] or null
     int T, N, K;                    // N = output features (SwiGLU: intermediate size)
     int up_row0;                    // SwiGLU: row of w where the up rows start
+    int gate;                       // gated epilogue: 1 = SiLU on the gate, 2 = GELU (tanh form)
     int kblocks_per_split;
     int out_f32;
     int* error;
@@ -249,7 +250,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // the library path rounds gate and up to bfloat16 before the activation; do the same
             const float g = __bfloat162float(__float2bfloat16_rn(acc));
             const float u = __bfloat162float(__float2bfloat16_rn(acc_up));
-            out = (g / (1.0f + expf(-g))) * u;
+            out = (p.gate == 2 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                               : g / (1.0f + expf(-g))) * u;
         } else {
             out = acc + (p.bias ? __bfloat162float(p.bias[n]) : 0.f);
         }
@@ -324,12 +326,13 @@ int fsie_gemm_decode_weight_map(void* map_out, const void* w, long long rows, lo
     return rc;
 }
 
-// y[T, N] = x[T, K] * w^T (+ bias), or for swiglu y[T, N] = silu(x w_gate^T) * (x w_up^T) with
-// w = [gate rows (N); up rows (N)].  T <= 64.  `splits` (1, 2, 4 or 8) cuts K over a cluster.
+// y[T, N] = x[T, K] * w^T (+ bias), or for swiglu != 0 y[T, N] = act(x w_gate^T) * (x w_up^T) with
+// w = [gate rows (N); up rows (N)], act = SiLU (swiglu = 1) or the tanh form of GELU (2).  T <= 64.  `splits` (1, 2, 4 or 8) cuts K over a cluster.
 int fsie_gemm_decode(const void* weight_map, const void* x, int ldx, void* y, int ldy, const void* bias,
                      int T, int N, int K, int swiglu, int out_f32, int splits, int* error, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
-    if (T > 64 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (splits != 1 && splits != 2 && splits != 4 && splits != 8))
+    if (T > 64 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (splits != 1 && splits != 2 && splits != 4 && splits != 8) ||
+        swiglu < 0 || swiglu > 2)
         return ERR_BAD_ARGUMENT;
     const int TN = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
     CUtensorMap map_w, map_x;
@@ -338,7 +341,7 @@ int fsie_gemm_decode(const void* weight_map, const void* x, int ldx, void* y, in
     if (rc != 0) return rc;
     GemmParams p;
     p.y = y; p.ldy = ldy; p.bias = (const bf16*)bias; p.T = T; p.N = N; p.K = K;
-    p.up_row0 = N; p.out_f32 = out_f32; p.error = error;
+    p.up_row0 = N; p.out_f32 = out_f32; p.error = error; p.gate = swiglu;
     const int total_kblocks = (K + BK - 1) / BK;
     p.kblocks_per_split = (total_kblocks + splits - 1) / splits;
     const int tiles = swiglu ? (N + BM / 2 - 1) / (BM / 2) : (N + BM - 1) / BM;

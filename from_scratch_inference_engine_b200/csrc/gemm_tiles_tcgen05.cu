@@ -61,6 +61,11 @@ constexpr uint32_t FIRST_BLOCK_MASK = 0xFEFFFFFFu;       // clears the bit of a 
                                                          // tells the second block of a pair from the first
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh_gate(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 enum { ERR_TMA_WAIT = 21, ERR_MMA_WAIT = 22, ERR_ACC_WAIT = 23, ERR_EPILOGUE_WAIT = 24 };
 
 struct TileGemmParams {
@@ -68,6 +73,7 @@ struct TileGemmParams {
     const bf16* bias;               // [N] or null
     int M, N, K;                    // N = output features (SwiGLU: the intermediate size)
     int up_row0;                    // SwiGLU: row of w where the up rows start
+    int gate;                       // gated epilogue: 1 = SiLU on the gate, 2 = GELU (tanh form)
     int m_tiles, n_tiles;
     int out_f32;
     int tma_store;                  // y is written through map_y (bf16, rows on 16-byte boundaries)
@@ -476,7 +482,7 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                         const float uj = __bfloat162float(__float2bfloat16_rn(u[j]));
                         // (approximate division: exact to 2 ulp of float, and without the slow path that
                         // the exact one takes when exp overflows the denominator; the quotient is 0 there)
-                        v[j] = __fdividef(gj, 1.0f + expf(-gj)) * uj;
+                        v[j] = (p.gate == 2 ? gelu_tanh_gate(gj) : __fdividef(gj, 1.0f + expf(-gj))) * uj;
                     }
                 } else {
                     tmem_load_32(trow + col, v);
@@ -708,8 +714,8 @@ int fsie_gemm_tiles_workspace(int M, int N, int K, int swiglu, int blocks, long 
     return plan(M, N, K, swiglu, blocks, p, &pairs, floats, counters);
 }
 
-// y[M, N] = x[M, K] * w^T (+ bias), or for swiglu y[M, N] = silu(x w_gate^T) * (x w_up^T) with
-// w = [gate rows (N); up rows (N)].  `blocks` is the size of the persistent grid (the number
+// y[M, N] = x[M, K] * w^T (+ bias), or for swiglu != 0 y[M, N] = act(x w_gate^T) * (x w_up^T) with
+// w = [gate rows (N); up rows (N)] and act = SiLU (swiglu = 1) or the tanh form of GELU (2).  `blocks` is the size of the persistent grid (the number
 // of SMs; it is cut to the pairs that can run at once and to the number of tiles).  workspace and
 // counters: see fsie_gemm_tiles_workspace; with less than that (or null) every tile is summed by
 // one pair, as if the last round were full.
@@ -717,7 +723,7 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
                     int M, int N, int K, int swiglu, int out_f32, int blocks, float* workspace,
                     long long workspace_floats, int* counters, int counters_len, int* error, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || blocks <= 0 || (swiglu && out_f32))
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || blocks <= 0 || (swiglu && out_f32) || swiglu < 0 || swiglu > 2)
         return ERR_BAD_ARGUMENT;
     CUtensorMap map_w, map_x;
     memcpy(&map_w, weight_map, sizeof(map_w));
@@ -732,7 +738,7 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
         p.share_pairs = 0;
     p.workspace = workspace; p.counters = counters;
     p.y = y; p.ldy = ldy; p.bias = (const bf16*)bias;
-    p.up_row0 = N; p.out_f32 = out_f32; p.error = error;
+    p.up_row0 = N; p.out_f32 = out_f32; p.error = error; p.gate = swiglu;
     // the copy engine writes y when its rows start on 16-byte boundaries; else the lanes store their rows
     p.tma_store = !out_f32 && ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
     CUtensorMap map_y = map_x;

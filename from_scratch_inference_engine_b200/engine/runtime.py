@@ -134,7 +134,8 @@ class Runtime:
             self._tables[key] = make().to(self.device).contiguous()
         return self._tables[key]
 
-    def prepare_weight(self, weight: torch.Tensor, swiglu: bool = False) -> None:
+    def prepare_weight(self, weight: torch.Tensor, swiglu: bool = False,
+                       activation: str = "silu") -> None:
         """Called by a part at bind for a matrix it will multiply activations with.  Large
         bfloat16 matrices get a TMA descriptor for the tcgen05 product that steps of few
         tokens use (the library product is kept where it measured faster: small matrices)."""
@@ -144,9 +145,9 @@ class Runtime:
         if k % 8 or (swiglu and rows % 2):
             return
         if self.products == "own":
-            self._tiled_weights[weight.data_ptr()] = (weight, swiglu)
+            self._tiled_weights[weight.data_ptr()] = (weight, swiglu, activation)
         if rows * k >= self.few_token_min_elements:
-            self._few_token_weights[weight.data_ptr()] = ops.DecodeWeight(weight, swiglu)
+            self._few_token_weights[weight.data_ptr()] = ops.DecodeWeight(weight, swiglu, activation)
 
     def _tiled(self, x: torch.Tensor, weight: torch.Tensor) -> Optional["ops.TiledWeight"]:
         """The weight's descriptor for the tiled product when this step is one for it: more
@@ -162,7 +163,8 @@ class Runtime:
         if ops.gemm_tiles_count(x.shape[0], n, swiglu) < least:
             return None
         if not known:
-            prepared = self._tiled_weights[weight.data_ptr()] = ops.TiledWeight(prepared[0], swiglu)
+            prepared = self._tiled_weights[weight.data_ptr()] = ops.TiledWeight(prepared[0], swiglu,
+                                                                                 prepared[2])
         return prepared
 
     def _tiled_product(self, prepared, x, bias, out_dtype, tag=None) -> torch.Tensor:
@@ -245,16 +247,13 @@ class Runtime:
                       activation: str = "silu") -> torch.Tensor:
         """silu(x @ gate.T) * (x @ up.T) for the stacked weight [gate rows; up rows]: one fused
         kernel for steps of few tokens, else the library product and the SwiGLU kernel.  With a
-        `bias` (stacked like the weight) the product adds it and the SwiGLU kernel follows.  With
-        another `activation` on the gate the stacked product is followed by the kernel of gated
-        activations."""
-        if activation != "silu":
-            both = self.linear(x, gate_up, bias, None if tag is None else tag + ".gate_up")
-            return ops.gated_act(both, self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype),
-                                 activation)
+        `bias` (stacked like the weight) the product adds it and the SwiGLU kernel follows.
+        `activation` names what the gate passes through (the fused kernels were told at
+        `prepare_weight`; the unfused path runs the kernel of gated activations)."""
         if bias is not None:
             both = self.linear(x, gate_up, bias, None if tag is None else tag + ".gate_up")
-            return ops.swiglu(both, self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype))
+            return self._gated(both, self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype),
+                               activation)
         prepared = self._few_tokens(x, gate_up) if self.dtype is torch.bfloat16 else None
         if prepared is not None and prepared.swiglu:
             return self._few_token_product(prepared, x, None, torch.bfloat16, tag)
@@ -264,7 +263,13 @@ class Runtime:
         wide = None if tag is None else tag + ".gate_up"
         both = self.linear(x, gate_up, None, wide) if prepared is None else F.linear(x, gate_up)
         act = self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype)
-        return ops.swiglu(both, act)
+        return self._gated(both, act, activation)
+
+    @staticmethod
+    def _gated(both: torch.Tensor, act: torch.Tensor, activation: str) -> torch.Tensor:
+        if activation == "silu":
+            return ops.swiglu(both, act)
+        return ops.gated_act(both, act, activation)
 
     def linear_f32_out(self, x: torch.Tensor, weight: torch.Tensor,
                        tag: Optional[str] = None) -> torch.Tensor:

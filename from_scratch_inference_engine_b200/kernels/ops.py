@@ -16,6 +16,7 @@ import torch
 from ..csrc import build
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
+GATE_KINDS = {"silu": 0, "gelu_tanh": 1}       # activations a gated feed-forward may put on its gate
 
 
 class KernelError(RuntimeError):
@@ -503,8 +504,9 @@ class DecodeWeight:
     """A bfloat16 weight [rows, K] prepared for `gemm_decode`: its TMA descriptor.
     For SwiGLU the weight holds the gate rows and then as many up rows."""
 
-    def __init__(self, weight: torch.Tensor, swiglu: bool = False):
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False, activation: str = "silu"):
         _need(weight, torch.bfloat16, "weight")
+        self.gate = 1 + GATE_KINDS[activation] if swiglu else 0     # what the kernel is told
         rows, k = weight.shape
         if k % 8:
             raise KernelError("gemm_decode: K must be a multiple of 8")
@@ -544,7 +546,7 @@ def gemm_decode(weight: DecodeWeight, x: torch.Tensor, out: torch.Tensor,
         _need(bias, torch.bfloat16, "bias")
     _check(gemm_decode_lib().fsie_gemm_decode(
         weight.map_ptr, _ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(bias), tokens,
-        weight.n, k, int(weight.swiglu), int(out.dtype is torch.float32), splits, _ptr(error),
+        weight.n, k, weight.gate, int(out.dtype is torch.float32), splits, _ptr(error),
         _stream()), "gemm_decode")
     return out
 
@@ -668,8 +670,9 @@ class TiledWeight:
     """A bfloat16 weight [rows, K] prepared for `gemm_tiles`: its TMA descriptor (boxes of 128
     rows).  For SwiGLU the weight holds the gate rows and then as many up rows."""
 
-    def __init__(self, weight: torch.Tensor, swiglu: bool = False):
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False, activation: str = "silu"):
         _need(weight, torch.bfloat16, "weight")
+        self.gate = 1 + GATE_KINDS[activation] if swiglu else 0     # what the kernel is told
         rows, k = weight.shape
         if k % 8:
             raise KernelError("gemm_tiles: K must be a multiple of 8")
@@ -723,7 +726,7 @@ def gemm_tiles(weight: TiledWeight, x: torch.Tensor, out: torch.Tensor,
         _need(counters, torch.int32, "counters")
     _check(gemm_tiles_lib().fsie_gemm_tiles(
         weight.map_ptr, _ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(bias), rows,
-        weight.n, k, int(weight.swiglu), int(out.dtype is torch.float32), blocks,
+        weight.n, k, weight.gate, int(out.dtype is torch.float32), blocks,
         _ptr(workspace), workspace.numel() if workspace is not None else 0,
         _ptr(counters), counters.numel() if counters is not None else 0, _ptr(error),
         _stream()), "gemm_tiles")
@@ -1164,9 +1167,6 @@ def norm_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], delta_gain: Op
                                        _ptr(rows), count, hidden, float(delta_eps), float(eps),
                                        int(write_x), _tag(dtype), _stream()), "norm_add_norm")
     return out
-
-
-GATE_KINDS = {"silu": 0, "gelu_tanh": 1}
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:

@@ -64,7 +64,7 @@ class SwiGluMlp(Part):
             self.b_down = tensors[self._name("down", "bias")].to(runtime.dtype).contiguous()
         # the fused SwiGLU products take no bias: with one, the stacked product adds it and a
         # kernel of its own applies the activation
-        runtime.prepare_weight(self.w_gate_up, swiglu=not self.bias and self.activation == "silu")
+        runtime.prepare_weight(self.w_gate_up, swiglu=not self.bias, activation=self.activation)
         runtime.prepare_weight(self.w_down)
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:

@@ -118,6 +118,29 @@ def test_gated_activation_against_the_formula():
     assert torch.allclose(plain.gelu_tanh(z), torch.nn.functional.gelu(z, approximate="tanh"))
 
 
+@pytest.mark.parametrize("rows,inter,k", [(300, 320, 512), (77, 100, 264), (8, 320, 512), (3, 100, 264)])
+def test_products_with_the_gelu_gate_in_their_epilogue(rows, inter, k):
+    """The tcgen05 products that apply the gate in their epilogue (tiles for many tokens, the
+    few-token form up to 64) with the tanh form of GELU instead of SiLU."""
+    import math
+    from from_scratch_inference_engine_b200.kernels import ops
+    torch.manual_seed(inter + rows)
+    x = (torch.randn(rows, k) * 1.5).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * inter, k) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    both = (x.double() @ w.double().T).to(torch.bfloat16).double()       # rounded as the unfused path
+    want = plain.gelu_tanh(both[:, :inter]) * both[:, inter:]
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    if rows > 64:
+        ops.gemm_tiles(ops.TiledWeight(w, swiglu=True, activation="gelu_tanh"), x, out, None, error, 148)
+    else:
+        ops.gemm_decode(ops.DecodeWeight(w, swiglu=True, activation="gelu_tanh"), x, out, None, error, 1)
+    assert error.item() == 0
+    assert (out.double() - want).abs().max().item() < 2.5e-2 * want.abs().max().item()
+    unfused = ops.gated_act(both.to(torch.bfloat16).cuda(), torch.empty_like(out), "gelu_tanh")
+    assert (out.double() - unfused.double()).abs().max().item() < 2.5e-2 * want.abs().max().item()
+
+
 @pytest.mark.parametrize("width", [19, 128, 200])
 def test_mingru_carries_state_between_calls(width):
     """Two requests of unequal length in one call, then more tokens of both in a second call (one
