@@ -207,6 +207,286 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_kernel(const S
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (mma.sync m16n8k16, bfloat16 operands, 32-bit sums) for
+// key sizes that are multiples of 16 and value sizes of 64, 128, 192, 256, 384 or 512.  A block
+// owns the same tile of up to 32 query rows; its eight warps are two groups of 16 rows times four
+// quarters.  Of a tile of 64 keys a warp first forms the scores of its 16 rows with ITS 16 keys
+// over the whole key size, the four quarters exchange the rows' maxima through shared memory, the
+// weights e^(s - m) go to shared memory as two bfloat16 halves (the weight and what rounding it
+// lost, so that they stay 32-bit weights), and then the warp adds all 64 keys into ITS quarter of
+// the value columns - with values 512 wide a warp still holds only 16 x 128 sums.  Keys and values
+// come by cp.async into two slots: the next tile travels while this one is multiplied.
+constexpr int TM_KT = 64;          // keys per tile
+constexpr int TM_PAD = 8;          // elements between rows in shared memory beyond their width
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 16 bytes from global to shared memory; zeros when `valid` is false (nothing is read then)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+struct MmaLayout {
+    int ldk, ldv, ldp;
+    size_t q_bytes, k_bytes, v_bytes, p_bytes, total;
+    __host__ __device__ MmaLayout(int dk, int dv, bool shared_v) {
+        ldk = dk + TM_PAD; ldv = dv + TM_PAD; ldp = TM_KT + TM_PAD;
+        q_bytes = (size_t)SA_ROWS * ldk * 2;
+        k_bytes = (size_t)2 * TM_KT * ldk * 2;
+        v_bytes = shared_v ? 0 : (size_t)2 * TM_KT * ldv * 2;
+        p_bytes = (size_t)2 * SA_ROWS * ldp * 2;
+        total = q_bytes + k_bytes + v_bytes + p_bytes + 2 * SA_ROWS * 4 * sizeof(float) + 2 * TM_KT * sizeof(int);
+    }
+};
+
+template <int NV, bool SHARED_V>
+__global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(const ScaledAttnParams p) {
+    extern __shared__ __align__(16) unsigned char tm_smem[];
+    const int dk = p.key_dim, dv = p.value_dim;
+    const MmaLayout L(dk, dv, SHARED_V);
+    bf16* Qs = reinterpret_cast<bf16*>(tm_smem);                                   // [32][ldk]
+    bf16* Ks = reinterpret_cast<bf16*>(tm_smem + L.q_bytes);                       // [2][64][ldk]
+    bf16* Vs = reinterpret_cast<bf16*>(tm_smem + L.q_bytes + L.k_bytes);           // [2][64][ldv]
+    bf16* Ph = reinterpret_cast<bf16*>(tm_smem + L.q_bytes + L.k_bytes + L.v_bytes);   // [32][ldp] weights
+    bf16* Pl = Ph + SA_ROWS * L.ldp;                                               //           and what rounding lost
+    float* pmax = reinterpret_cast<float*>(Pl + SA_ROWS * L.ldp);                  // [32][4]
+    float* psum = pmax + SA_ROWS * 4;                                              // [32][4]
+    int* key_ok = reinterpret_cast<int*>(psum + SA_ROWS * 4);                      // [2][64]
+
+    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
+    const int group = p.heads / p.kv_heads;
+    grid_dependency_wait();
+    grid_dependents_go();
+    const int item = p.tile_item[tile];
+    if (p.item_slots && p.item_slots[item] < 0) return;
+    const int row0 = p.tile_row0[tile];
+    const int qstart = p.item_qstart[item], qlen = p.item_qlen[item], pos0 = p.item_pos0[item];
+    const int nrows = min(SA_ROWS, qlen * group - row0);
+    if (nrows <= 0) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int mi = warp >> 2, vi = warp & 3;             // which 16 rows; which quarter of keys / value columns
+    const int g = lane >> 2, t = lane & 3;
+    const bf16* q = (const bf16*)p.q;
+    const bf16* kp = (const bf16*)p.k_pages;
+    const bf16* vp = (const bf16*)p.v_pages;
+    const int* bt = p.block_tables + (size_t)item * p.bt_stride;
+
+    const int pos_first = pos0 + row0 / group;
+    const int pos_last = pos0 + (row0 + nrows - 1) / group;
+    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kend = pos_last + 1;
+    if (p.nsplit > 1) {
+        const int span = kend - kbegin;
+        int chunk = (span + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + TM_KT - 1) / TM_KT) * TM_KT;
+        const int b = kbegin + split * chunk;
+        kend = min(kend, b + chunk);
+        kbegin = b;
+    }
+
+    // one tile of keys (and values) on its way into slot `stage`: a warp copies eight rows
+    auto issue_tile = [&](int stage, int k0) {
+        for (int j = warp; j < TM_KT; j += SA_WARPS) {
+            const int kj = k0 + j;
+            int page = -1;
+            if (kj < kend) {
+                page = bt[kj / p.page_size];
+                if (page < 0 && lane == 0 && p.error && kj <= pos_last &&
+                    (p.window <= 0 || kj > pos_first - p.window))
+                    atomicExch(p.error, 3);        // some row of the tile sees this key, and its page was given back
+            }
+            const bool ok = page >= 0;
+            const long long at = (long long)kvh * p.page_size + kj % p.page_size;
+            const bf16* ksrc = kp + (ok ? (long long)page * p.page_stride + at * dk : 0);
+            bf16* kdst = Ks + ((size_t)stage * TM_KT + j) * L.ldk;
+            for (int c = lane; c < dk / 8; c += 32) cp_async16(kdst + c * 8, ksrc + c * 8, ok);
+            if (!SHARED_V) {
+                const bf16* vsrc = vp + (ok ? (long long)page * p.page_stride + at * p.value_ld : 0);
+                bf16* vdst = Vs + ((size_t)stage * TM_KT + j) * L.ldv;
+                for (int c = lane; c < dv / 8; c += 32) cp_async16(vdst + c * 8, vsrc + c * 8, ok);
+            }
+            if (lane == 0) key_ok[stage * TM_KT + j] = ok;
+        }
+        cp_async_commit();
+    };
+    if (kbegin < kend) issue_tile(0, kbegin);
+
+    // the tile's query rows as they are (the head's scale meets the scores), zero beyond the tile
+    for (int r = warp; r < SA_ROWS; r += SA_WARPS) {
+        const int row = row0 + r;
+        const bf16* src = q + (size_t)(qstart + row / group) * p.q_ld + (size_t)(kvh * group + row % group) * dk;
+        for (int c = lane; c < dk / 8; c += 32) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < nrows) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(Qs + r * L.ldk + c * 8) = v;
+        }
+    }
+
+    // this thread's two rows: g and g + 8 of its group of 16
+    int pos[2];
+    float sc[2], m[2], l[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = mi * 16 + g + 8 * i;
+        pos[i] = r < nrows ? pos0 + (row0 + r) / group : -1;
+        sc[i] = r < nrows ? p.head_scale[kvh * group + (row0 + r) % group] : 0.f;
+        m[i] = -INFINITY; l[i] = 0.f;
+    }
+    float acc[NV][4];
+#pragma unroll
+    for (int n = 0; n < NV; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    const int dvq = NV * 8;                              // value columns of this warp: vi * dvq ...
+    const int ldvv = SHARED_V ? L.ldk : L.ldv;
+
+    int it = 0;
+    for (int k0 = kbegin; k0 < kend; k0 += TM_KT, ++it) {
+        const int stage = it & 1;
+        cp_async_wait_all();
+        __syncthreads();                 // this tile has arrived; everybody is done with the tile before it
+        if (k0 + TM_KT < kend) issue_tile(stage ^ 1, k0 + TM_KT);
+        // ---- scores of 16 rows x 16 keys over the whole key size
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        {
+            const bf16* qa = Qs + (mi * 16 + (lane & 15)) * L.ldk + (lane >> 4) * 8;
+            const bf16* kb = Ks + ((size_t)stage * TM_KT + vi * 16 + (lane & 7) + (lane >> 4) * 8) * L.ldk + ((lane >> 3) & 1) * 8;
+            for (int kk = 0; kk < dk; kk += 16) {
+                uint32_t a[4], b[4];
+                ldsm_x4(a, qa + kk);
+                ldsm_x4(b, kb + kk);
+                mma_bf16(s[0], a, b[0], b[1]);
+                mma_bf16(s[1], a, b[2], b[3]);
+            }
+        }
+        bool seen[2][4];
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int j = vi * 16 + n * 8 + 2 * t + (e & 1);
+                const int kj = k0 + j;
+                seen[n][e] = key_ok[stage * TM_KT + j] && kj <= pos[i] && (p.window <= 0 || kj > pos[i] - p.window);
+                s[n][e] = seen[n][e] ? s[n][e] * sc[i] : -INFINITY;
+                tmax[i] = fmaxf(tmax[i], s[n][e]);
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+            tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+            if (t == 0) pmax[(mi * 16 + g + 8 * i) * 4 + vi] = tmax[i];
+        }
+        __syncthreads();                 // the four quarters' maxima of every row
+        float corr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float4 q4 = *reinterpret_cast<const float4*>(pmax + (mi * 16 + g + 8 * i) * 4);
+            const float m_new = fmaxf(m[i], fmaxf(fmaxf(q4.x, q4.y), fmaxf(q4.z, q4.w)));
+            corr[i] = m_new == -INFINITY ? 1.f : expf(m[i] - m_new);
+            m[i] = m_new;
+            l[i] *= corr[i];
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            float pw[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                pw[e] = seen[n][e] ? expf(s[n][e] - m[e >> 1]) : 0.f;
+                l[e >> 1] += pw[e];
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(pw[2 * i], pw[2 * i + 1]);
+                const float2 back = __bfloat1622float2(hi);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(pw[2 * i] - back.x, pw[2 * i + 1] - back.y);
+                const int at = (mi * 16 + g + 8 * i) * L.ldp + vi * 16 + n * 8 + 2 * t;
+                *reinterpret_cast<__nv_bfloat162*>(Ph + at) = hi;
+                *reinterpret_cast<__nv_bfloat162*>(Pl + at) = lo;
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            acc[n][0] *= corr[0]; acc[n][1] *= corr[0];
+            acc[n][2] *= corr[1]; acc[n][3] *= corr[1];
+        }
+        __syncthreads();                 // the weights of all 64 keys
+        // ---- 16 rows x this warp's value columns += weights x values, for both halves of the weights
+        {
+            const bf16* pa = Ph + (mi * 16 + (lane & 15)) * L.ldp + (lane >> 4) * 8;
+            const bf16* pb = Pl + (mi * 16 + (lane & 15)) * L.ldp + (lane >> 4) * 8;
+            const bf16* vbase = (SHARED_V ? Ks + (size_t)stage * TM_KT * L.ldk : Vs + (size_t)stage * TM_KT * L.ldv) +
+                                ((lane & 7) + ((lane >> 3) & 1) * 8) * ldvv + vi * dvq + (lane >> 4) * 8;
+#pragma unroll
+            for (int kk = 0; kk < TM_KT; kk += 16) {
+                uint32_t ah[4], al[4];
+                ldsm_x4(ah, pa + kk);
+                ldsm_x4(al, pb + kk);
+#pragma unroll
+                for (int np = 0; np < NV / 2; ++np) {
+                    uint32_t b[4];
+                    ldsm_x4_trans(b, vbase + (size_t)kk * ldvv + np * 16);
+                    mma_bf16(acc[2 * np], ah, b[0], b[1]);
+                    mma_bf16(acc[2 * np], al, b[0], b[1]);
+                    mma_bf16(acc[2 * np + 1], ah, b[2], b[3]);
+                    mma_bf16(acc[2 * np + 1], al, b[2], b[3]);
+                }
+            }
+        }
+    }
+
+    // the rows' sums: over the four lanes that share a row, then over the four quarters
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        if (t == 0) psum[(mi * 16 + g + 8 * i) * 4 + vi] = l[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = mi * 16 + g + 8 * i;
+        if (r >= nrows) continue;
+        const float4 q4 = *reinterpret_cast<const float4*>(psum + r * 4);
+        const float total = (q4.x + q4.y) + (q4.z + q4.w);
+        const int row = row0 + r;
+        const int tok = qstart + row / group, h = kvh * group + row % group;
+        if (p.nsplit == 1) {
+            const float inv = total > 0.f ? 1.0f / total : 0.f;
+            bf16* o = (bf16*)p.out + (size_t)tok * p.out_ld + (size_t)h * dv + vi * dvq + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NV; ++n)
+                *reinterpret_cast<__nv_bfloat162*>(o + n * 8) =
+                    __floats2bfloat162_rn(acc[n][2 * i] * inv, acc[n][2 * i + 1] * inv);
+        } else {
+            const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
+            float* o = p.part_o + idx * dv + vi * dvq + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NV; ++n)
+                *reinterpret_cast<float2*>(o + n * 8) = make_float2(acc[n][2 * i], acc[n][2 * i + 1]);
+            if (vi == 0 && t == 0) { p.part_ml[idx * 2] = m[i]; p.part_ml[idx * 2 + 1] = total; }
+        }
+    }
+}
+
 // o = sum_z acc_z e^(m_z - M) / sum_z l_z e^(m_z - M) over the key ranges z of one (token, head)
 template <typename T>
 __global__ void sa_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -321,6 +601,29 @@ static int scaled_attention_dispatch(const ScaledAttnParams& p, int tiles, bool 
     return ERR_UNSUPPORTED;
 }
 
+
+template <int NV>
+static int scaled_attention_mma_launch(const ScaledAttnParams& p, int tiles, bool shared_v, cudaStream_t stream) {
+    const size_t smem = MmaLayout(p.key_dim, p.value_dim, shared_v).total;
+    const dim3 grid(p.kv_heads, tiles, p.nsplit);
+    if (shared_v) {
+        cudaFuncSetAttribute(scaled_attention_mma_kernel<NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return launch_dependent(scaled_attention_mma_kernel<NV, true>, grid, dim3(SA_WARPS * 32), smem, stream, p);
+    }
+    cudaFuncSetAttribute(scaled_attention_mma_kernel<NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_dependent(scaled_attention_mma_kernel<NV, false>, grid, dim3(SA_WARPS * 32), smem, stream, p);
+}
+
+// whether the tensor-core form takes these sizes and addresses
+static bool scaled_attention_mma_takes(const ScaledAttnParams& p, int dtype, bool shared_v) {
+    const int dv = p.value_dim;
+    if (dtype != DTYPE_BF16 || p.key_dim % 16 || !(dv == 64 || dv == 128 || dv == 192 || dv == 256 || dv == 384 || dv == 512))
+        return false;
+    if (p.page_stride % 8 || p.q_ld % 8 || p.out_ld % 2 || p.value_ld % 8) return false;
+    if (((size_t)p.q | (size_t)p.k_pages | (size_t)p.v_pages) & 15 || ((size_t)p.out & 3)) return false;
+    return MmaLayout(p.key_dim, dv, shared_v).total <= 227 * 1024;
+}
+
 }  // namespace fsie
 
 using namespace fsie;
@@ -330,6 +633,8 @@ extern "C" {
 int fsie_scaled_attention_rows() { return SA_ROWS; }
 
 // values_in_keys != 0: v_pages is ignored, a key row's first value_dim columns are its value row.
+// form 0: the tensor-core kernel where it takes the sizes (bfloat16), else the 32-bit one; 1: the
+// 32-bit kernel; 2: the tensor-core kernel or refusal.
 // With nsplit > 1 the caller gives part_o [nsplit, tokens, heads, value_dim] and part_ml
 // [nsplit, tokens, heads, 2] (float); the ranges are merged after the launch.
 int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, const void* k_pages,
@@ -338,7 +643,7 @@ int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, cons
                           const int* tile_item, const int* tile_row0, int tiles, const int* item_qstart,
                           const int* item_qlen, const int* item_pos0, const int* item_slots, void* out,
                           int out_ld, float* part_o, float* part_ml, int tokens, int heads, int kv_heads,
-                          int window, int nsplit, int dtype, int* error, cudaStream_t stream) {
+                          int window, int nsplit, int dtype, int form, int* error, cudaStream_t stream) {
     if (tokens <= 0 || tiles <= 0) return 0;
     if (tiles > 65535 || nsplit > 65535) return ERR_UNSUPPORTED;
     if (key_dim <= 0 || value_dim <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 ||
@@ -356,8 +661,22 @@ int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, cons
     p.out = out; p.out_ld = out_ld; p.part_o = part_o; p.part_ml = part_ml;
     p.tokens = tokens; p.heads = heads; p.kv_heads = kv_heads; p.window = window; p.nsplit = nsplit;
     p.error = error;
-    int rc = dtype == DTYPE_F32 ? scaled_attention_dispatch<float>(p, tiles, values_in_keys != 0, stream)
+    int rc;
+    if (form != 1 && scaled_attention_mma_takes(p, dtype, values_in_keys != 0)) {
+        switch (value_dim / 32) {
+            case 2: rc = scaled_attention_mma_launch<2>(p, tiles, values_in_keys != 0, stream); break;
+            case 4: rc = scaled_attention_mma_launch<4>(p, tiles, values_in_keys != 0, stream); break;
+            case 6: rc = scaled_attention_mma_launch<6>(p, tiles, values_in_keys != 0, stream); break;
+            case 8: rc = scaled_attention_mma_launch<8>(p, tiles, values_in_keys != 0, stream); break;
+            case 12: rc = scaled_attention_mma_launch<12>(p, tiles, values_in_keys != 0, stream); break;
+            default: rc = scaled_attention_mma_launch<16>(p, tiles, values_in_keys != 0, stream); break;
+        }
+    } else if (form == 2) {
+        return ERR_UNSUPPORTED;
+    } else {
+        rc = dtype == DTYPE_F32 ? scaled_attention_dispatch<float>(p, tiles, values_in_keys != 0, stream)
                                 : scaled_attention_dispatch<bf16>(p, tiles, values_in_keys != 0, stream);
+    }
     if (rc != 0 || nsplit == 1) return rc;
     const dim3 cgrid(tokens, heads);
     const int threads = value_dim >= 128 ? 128 : (value_dim >= 64 ? 64 : 32);

@@ -1120,7 +1120,7 @@ def mixers():
         lib.fsie_mingru_scan.argtypes = [p, i, i, p, p, p, i, p, p, i, i, p, p, p, p, i, p]
         lib.fsie_scaled_attention_rows.argtypes = []
         lib.fsie_scaled_attention.argtypes = [p, i, p, p, p, ll, i, i, i, i, p, i, p, p, i, p, p, p, p,
-                                              p, i, p, p, i, i, i, i, i, i, p, p]
+                                              p, i, p, p, i, i, i, i, i, i, i, p, p]
         lib.fsie_rotate_mix_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p,
                                               i, p, p]
         lib.fsie_latent_prep.argtypes = [p, i, p, p, i, p, p, ll, i, p, f, p, i, i, i, i, i, i, i, p, p]
@@ -1219,10 +1219,12 @@ def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pag
                      item_slots: Optional[torch.Tensor], out: torch.Tensor, tokens: int, heads: int,
                      kv_heads: int, window: int, error: torch.Tensor, nsplit: int = 1,
                      part_o: Optional[torch.Tensor] = None,
-                     part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     part_ml: Optional[torch.Tensor] = None, form: str = "auto") -> torch.Tensor:
     """Causal (optionally windowed) softmax attention of q [tokens, heads x key_dim] over paged keys
     [kv_head][slot][key_dim] and values [kv_head][slot][value_dim] (or, values_in_keys, the first
-    value_dim columns of the key rows), scores multiplied by head_scale[head]; 32-bit arithmetic."""
+    value_dim columns of the key rows), scores multiplied by head_scale[head]; scores, softmax and
+    weights in 32-bit.  `form`: "auto" takes the tensor-core kernel where it fits (bfloat16, key
+    sizes in steps of 16, value sizes 64 ... 512), "plain" the 32-bit kernel, "mma" insists."""
     _need(q, None, "q", contiguous=False)
     _need(head_scale, torch.float32, "head_scale")
     _need(out, q.dtype, "out")
@@ -1239,7 +1241,8 @@ def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pag
         value_dim, int(values_in_keys), _ptr(block_tables), block_tables.stride(0), _ptr(tile_item),
         _ptr(tile_row0), tiles, _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots),
         _ptr(out), heads * value_dim, _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, window,
-        nsplit, _tag(q.dtype), _ptr(error), _stream()), "scaled_attention")
+        nsplit, _tag(q.dtype), {"auto": 0, "plain": 1, "mma": 2}[form], _ptr(error), _stream()),
+        "scaled_attention")
     return out
 
 

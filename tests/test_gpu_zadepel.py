@@ -208,17 +208,25 @@ def _paged(rows, page_size, order, pages_total, width, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,shared", [(0, False), (37, False), (0, True), (45, True)])
-def test_scaled_attention_far_keys_page_borders_and_window_edges(dtype, window, shared):
+@pytest.mark.parametrize("sizes", ["small", "tensor cores"])
+@pytest.mark.parametrize("window,shared", [(0, False), (37, False), (0, True), (45, True), (70, True)])
+def test_scaled_attention_far_keys_page_borders_and_window_edges(dtype, window, shared, sizes):
     """Keys in shuffled pages, a request of 300 cached tokens that brings 77 more (a portion) and
     another that decodes one token at position 260, whole and split over five key ranges.  For
     chosen queries one key is made to stand out - far back, on either side of a page border, the
     last one inside the window while the first one outside it would stand out even more - so that
     reading a wrong page or slot, or a window one key off, changes the output by the size of a
-    value.  `shared`: one key/value head whose values are the first columns of its key rows."""
+    value.  `shared`: one key/value head whose values are the first columns of its key rows.
+    `sizes`: key and value sizes that only the 32-bit kernel takes, or sizes that in bfloat16
+    the tensor-core kernel takes as well (then both forms run)."""
     from from_scratch_inference_engine_b200.kernels import ops
     g = torch.Generator().manual_seed(5 + window)
-    heads, kv_heads, dk, dv, page = 6, (1 if shared else 2), 24, (16 if shared else 40), 16
+    heads, kv_heads, page = 6, (1 if shared else 2), 16
+    if sizes == "small":
+        dk, dv = 24, (16 if shared else 40)
+    else:
+        dk, dv = (80, 64) if shared else (48, 128)
+    forms = ["plain", "mma"] if sizes != "small" and dtype is torch.bfloat16 else ["auto"]
     group = heads // kv_heads
     lengths = [(300, 77), (260, 1)]
     pages_total = sum(-(-(a + b) // page) for a, b in lengths) + 3
@@ -267,7 +275,7 @@ def test_scaled_attention_far_keys_page_borders_and_window_edges(dtype, window, 
     both = (k_pages if shared else torch.cat([k_pages, v_pages], dim=1)).cuda()
     keys = kv_heads * page * dk
     expect = torch.cat(want)
-    for nsplit in (1, 5):
+    for nsplit, form in [(n, f) for n in (1, 5) for f in forms]:
         out = torch.zeros(tokens, heads * dv, device="cuda", dtype=dtype)
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
         ops.scaled_attention(q, heads * dk, head_scale.float().cuda(), both[:, :keys],
@@ -275,11 +283,11 @@ def test_scaled_attention_far_keys_page_borders_and_window_edges(dtype, window, 
                              bt.cuda(), dev(item), dev(row0), len(item), dev([0, 77]), dev([77, 1]),
                              dev([300, 260]), dev([0, 1]), out, tokens, heads, kv_heads, window, error,
                              nsplit, torch.empty(nsplit * tokens * heads * dv, device="cuda"),
-                             torch.empty(nsplit * tokens * heads * 2, device="cuda"))
+                             torch.empty(nsplit * tokens * heads * 2, device="cuda"), form=form)
         assert int(error.item()) == 0
         got = out.cpu().double().reshape(tokens, heads, dv)
         tolerance = 2e-5 if dtype is torch.float32 else 2e-2
-        assert (got - expect).abs().max() < tolerance * max(1.0, float(expect.abs().max())), nsplit
+        assert (got - expect).abs().max() < tolerance * max(1.0, float(expect.abs().max())), (nsplit, form)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -530,7 +538,7 @@ def test_long_decoding_through_graphs_and_without(tmp_path_factory):
         assert_rows(rows, requests, folder, F32_BOUND)
         both.append(rows)
     for key in both[0]:
-        assert float(np.abs(both[0][key] - both[1][key]).max()) < 1e-5
+        assert float(np.abs(both[0][key] - both[1][key]).max()) < 0.25 * F32_BOUND
 
 
 def test_decode_batch_with_padding_leaves_other_slots_alone(tmp_path_factory):
