@@ -216,7 +216,8 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_kernel(const S
 // weights e^(s - m) go to shared memory as two bfloat16 halves (the weight and what rounding it
 // lost, so that they stay 32-bit weights), and then the warp adds all 64 keys into ITS quarter of
 // the value columns - with values 512 wide a warp still holds only 16 x 128 sums.  Keys and values
-// come by cp.async into two slots: the next tile travels while this one is multiplied.
+// come by cp.async into two slots: the next tile travels while this one is multiplied.  (A key whose
+// page was given back arrives as zeros and sets the error flag; the exponentials are the fast ones.)
 constexpr int TM_KT = 64;          // keys per tile
 constexpr int TM_PAD = 8;          // elements between rows in shared memory beyond their width
 
@@ -300,29 +301,30 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
         kbegin = b;
     }
 
-    // one tile of keys (and values) on its way into slot `stage`: a warp copies eight rows
+    // one tile of keys (and values) on its way into slot `stage`: THREADS / 64 threads share a row, so
+    // that all 64 page lookups are under way at once
     auto issue_tile = [&](int stage, int k0) {
-        for (int j = warp; j < TM_KT; j += SA_WARPS) {
-            const int kj = k0 + j;
-            int page = -1;
-            if (kj < kend) {
-                page = bt[kj / p.page_size];
-                if (page < 0 && lane == 0 && p.error && kj <= pos_last &&
-                    (p.window <= 0 || kj > pos_first - p.window))
-                    atomicExch(p.error, 3);        // some row of the tile sees this key, and its page was given back
-            }
-            const bool ok = page >= 0;
-            const long long at = (long long)kvh * p.page_size + kj % p.page_size;
-            const bf16* ksrc = kp + (ok ? (long long)page * p.page_stride + at * dk : 0);
-            bf16* kdst = Ks + ((size_t)stage * TM_KT + j) * L.ldk;
-            for (int c = lane; c < dk / 8; c += 32) cp_async16(kdst + c * 8, ksrc + c * 8, ok);
-            if (!SHARED_V) {
-                const bf16* vsrc = vp + (ok ? (long long)page * p.page_stride + at * p.value_ld : 0);
-                bf16* vdst = Vs + ((size_t)stage * TM_KT + j) * L.ldv;
-                for (int c = lane; c < dv / 8; c += 32) cp_async16(vdst + c * 8, vsrc + c * 8, ok);
-            }
-            if (lane == 0) key_ok[stage * TM_KT + j] = ok;
+        constexpr int TPR = (SA_WARPS * 32) / TM_KT;
+        const int j = tid / TPR, part = tid % TPR;
+        const int kj = k0 + j;
+        int page = -1;
+        if (kj < kend) {
+            page = bt[kj / p.page_size];
+            if (page < 0 && part == 0 && p.error && kj <= pos_last &&
+                (p.window <= 0 || kj > pos_first - p.window))
+                atomicExch(p.error, 3);            // some row of the tile sees this key, and its page was given back
         }
+        const bool ok = page >= 0;
+        const long long at = (long long)kvh * p.page_size + kj % p.page_size;
+        const bf16* ksrc = kp + (ok ? (long long)page * p.page_stride + at * dk : 0);
+        bf16* kdst = Ks + ((size_t)stage * TM_KT + j) * L.ldk;
+        for (int c = part; c < dk / 8; c += TPR) cp_async16(kdst + c * 8, ksrc + c * 8, ok);
+        if (!SHARED_V) {
+            const bf16* vsrc = vp + (ok ? (long long)page * p.page_stride + at * p.value_ld : 0);
+            bf16* vdst = Vs + ((size_t)stage * TM_KT + j) * L.ldv;
+            for (int c = part; c < dv / 8; c += TPR) cp_async16(vdst + c * 8, vsrc + c * 8, ok);
+        }
+        if (part == 0) key_ok[stage * TM_KT + j] = ok;
         cp_async_commit();
     };
     if (kbegin < kend) issue_tile(0, kbegin);
@@ -384,7 +386,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
                 const int i = e >> 1;
                 const int j = vi * 16 + n * 8 + 2 * t + (e & 1);
                 const int kj = k0 + j;
-                seen[n][e] = key_ok[stage * TM_KT + j] && kj <= pos[i] && (p.window <= 0 || kj > pos[i] - p.window);
+                seen[n][e] = kj < kend && kj <= pos[i] && (p.window <= 0 || kj > pos[i] - p.window);
                 s[n][e] = seen[n][e] ? s[n][e] * sc[i] : -INFINITY;
                 tmax[i] = fmaxf(tmax[i], s[n][e]);
             }
@@ -400,7 +402,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
         for (int i = 0; i < 2; ++i) {
             const float4 q4 = *reinterpret_cast<const float4*>(pmax + (mi * 16 + g + 8 * i) * 4);
             const float m_new = fmaxf(m[i], fmaxf(fmaxf(q4.x, q4.y), fmaxf(q4.z, q4.w)));
-            corr[i] = m_new == -INFINITY ? 1.f : expf(m[i] - m_new);
+            corr[i] = m_new == -INFINITY ? 1.f : __expf(m[i] - m_new);
             m[i] = m_new;
             l[i] *= corr[i];
         }
@@ -409,7 +411,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
             float pw[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                pw[e] = seen[n][e] ? expf(s[n][e] - m[e >> 1]) : 0.f;
+                pw[e] = seen[n][e] ? __expf(s[n][e] - m[e >> 1]) : 0.f;
                 l[e >> 1] += pw[e];
             }
 #pragma unroll
@@ -483,6 +485,234 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
             for (int n = 0; n < NV; ++n)
                 *reinterpret_cast<float2*>(o + n * 8) = make_float2(acc[n][2 * i], acc[n][2 * i + 1]);
             if (vi == 0 && t == 0) { p.part_ml[idx * 2] = m[i]; p.part_ml[idx * 2 + 1] = total; }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// The tensor-core form for value sizes up to 256: a warp owns 16 query rows with ALL their value
+// columns, so the weights never leave its registers (the score tile's accumulator layout is the
+// layout of the next product's first operand) and the warps of a block meet only where a tile of
+// keys changes hands.  A block is four warps = a tile of up to 64 query rows.
+constexpr int TR_ROWS = 64, TR_WARPS = 4;
+
+struct RowsLayout {
+    int ldk, ldv;
+    size_t q_bytes, k_bytes, v_bytes, total;
+    __host__ __device__ RowsLayout(int dk, int dv, bool shared_v) {
+        ldk = dk + TM_PAD; ldv = dv + TM_PAD;
+        q_bytes = (size_t)TR_ROWS * ldk * 2;
+        k_bytes = (size_t)2 * TM_KT * ldk * 2;
+        v_bytes = shared_v ? 0 : (size_t)2 * TM_KT * ldv * 2;
+        total = q_bytes + k_bytes + v_bytes + 2 * TM_KT * sizeof(int);
+    }
+};
+
+template <int NVT, bool SHARED_V>
+__global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(const ScaledAttnParams p) {
+    extern __shared__ __align__(16) unsigned char tr_smem[];
+    const int dk = p.key_dim, dv = p.value_dim;
+    const RowsLayout L(dk, dv, SHARED_V);
+    bf16* Qs = reinterpret_cast<bf16*>(tr_smem);                                   // [64][ldk]
+    bf16* Ks = reinterpret_cast<bf16*>(tr_smem + L.q_bytes);                       // [2][64][ldk]
+    bf16* Vs = reinterpret_cast<bf16*>(tr_smem + L.q_bytes + L.k_bytes);           // [2][64][ldv]
+    int* key_ok = reinterpret_cast<int*>(tr_smem + L.q_bytes + L.k_bytes + L.v_bytes);   // [2][64]
+
+    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
+    const int group = p.heads / p.kv_heads;
+    grid_dependency_wait();
+    grid_dependents_go();
+    const int item = p.tile_item[tile];
+    if (p.item_slots && p.item_slots[item] < 0) return;
+    const int row0 = p.tile_row0[tile];
+    const int qstart = p.item_qstart[item], qlen = p.item_qlen[item], pos0 = p.item_pos0[item];
+    const int nrows = min(TR_ROWS, qlen * group - row0);
+    if (nrows <= 0) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const bf16* q = (const bf16*)p.q;
+    const bf16* kp = (const bf16*)p.k_pages;
+    const bf16* vp = (const bf16*)p.v_pages;
+    const int* bt = p.block_tables + (size_t)item * p.bt_stride;
+
+    const int pos_first = pos0 + row0 / group;
+    const int pos_last = pos0 + (row0 + nrows - 1) / group;
+    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kend = pos_last + 1;
+    if (p.nsplit > 1) {
+        const int span = kend - kbegin;
+        int chunk = (span + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + TM_KT - 1) / TM_KT) * TM_KT;
+        const int b = kbegin + split * chunk;
+        kend = min(kend, b + chunk);
+        kbegin = b;
+    }
+
+    // one tile of keys (and values) on its way into slot `stage`: THREADS / 64 threads share a row, so
+    // that all 64 page lookups are under way at once
+    auto issue_tile = [&](int stage, int k0) {
+        constexpr int TPR = (TR_WARPS * 32) / TM_KT;
+        const int j = tid / TPR, part = tid % TPR;
+        const int kj = k0 + j;
+        int page = -1;
+        if (kj < kend) {
+            page = bt[kj / p.page_size];
+            if (page < 0 && part == 0 && p.error && kj <= pos_last &&
+                (p.window <= 0 || kj > pos_first - p.window))
+                atomicExch(p.error, 3);            // some row of the tile sees this key, and its page was given back
+        }
+        const bool ok = page >= 0;
+        const long long at = (long long)kvh * p.page_size + kj % p.page_size;
+        const bf16* ksrc = kp + (ok ? (long long)page * p.page_stride + at * dk : 0);
+        bf16* kdst = Ks + ((size_t)stage * TM_KT + j) * L.ldk;
+        for (int c = part; c < dk / 8; c += TPR) cp_async16(kdst + c * 8, ksrc + c * 8, ok);
+        if (!SHARED_V) {
+            const bf16* vsrc = vp + (ok ? (long long)page * p.page_stride + at * p.value_ld : 0);
+            bf16* vdst = Vs + ((size_t)stage * TM_KT + j) * L.ldv;
+            for (int c = part; c < dv / 8; c += TPR) cp_async16(vdst + c * 8, vsrc + c * 8, ok);
+        }
+        if (part == 0) key_ok[stage * TM_KT + j] = ok;
+        cp_async_commit();
+    };
+    if (kbegin < kend) issue_tile(0, kbegin);
+
+    for (int r = warp; r < TR_ROWS; r += TR_WARPS) {
+        const int row = row0 + r;
+        const bf16* src = q + (size_t)(qstart + row / group) * p.q_ld + (size_t)(kvh * group + row % group) * dk;
+        for (int c = lane; c < dk / 8; c += 32) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < nrows) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(Qs + r * L.ldk + c * 8) = v;
+        }
+    }
+
+    int pos[2];
+    float sc[2], m[2], l[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = warp * 16 + g + 8 * i;
+        pos[i] = r < nrows ? pos0 + (row0 + r) / group : -1;
+        sc[i] = r < nrows ? p.head_scale[kvh * group + (row0 + r) % group] : 0.f;
+        m[i] = -INFINITY; l[i] = 0.f;
+    }
+    // the latest position among this warp's rows: tiles of keys beyond it are none of its business
+    const int warp_rows = min(16, nrows - warp * 16);
+    const int warp_last = warp_rows > 0 ? pos0 + (row0 + warp * 16 + warp_rows - 1) / group : -1;
+    const int warp_first = warp_rows > 0 ? pos0 + (row0 + warp * 16) / group : 0;
+    float acc[NVT][4];
+#pragma unroll
+    for (int n = 0; n < NVT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    const int ldvv = SHARED_V ? L.ldk : L.ldv;
+
+    int it = 0;
+    for (int k0 = kbegin; k0 < kend; k0 += TM_KT, ++it) {
+        const int stage = it & 1;
+        cp_async_wait_all();
+        __syncthreads();                 // this tile has arrived; everybody is done with the tile before it
+        if (k0 + TM_KT < kend) issue_tile(stage ^ 1, k0 + TM_KT);
+        if (k0 > warp_last || (p.window > 0 && k0 + TM_KT - 1 <= warp_first - p.window)) continue;
+        // ---- scores of 16 rows x 64 keys
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        {
+            const bf16* qa = Qs + (warp * 16 + (lane & 15)) * L.ldk + (lane >> 4) * 8;
+            const bf16* kb = Ks + ((size_t)stage * TM_KT + (lane & 7) + (lane >> 4) * 8) * L.ldk + ((lane >> 3) & 1) * 8;
+            for (int kk = 0; kk < dk; kk += 16) {
+                uint32_t a[4];
+                ldsm_x4(a, qa + kk);
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) {
+                    uint32_t b[4];
+                    ldsm_x4(b, kb + (size_t)nb * 16 * L.ldk + kk);
+                    mma_bf16(s[2 * nb], a, b[0], b[1]);
+                    mma_bf16(s[2 * nb + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int j = n * 8 + 2 * t + (e & 1);
+                const int kj = k0 + j;
+                const bool seen = kj < kend && kj <= pos[i] && (p.window <= 0 || kj > pos[i] - p.window);
+                s[n][e] = seen ? s[n][e] * sc[i] : -INFINITY;
+                tmax[i] = fmaxf(tmax[i], s[n][e]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+            tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+            const float m_new = fmaxf(m[i], tmax[i]);
+            corr[i] = m_new == -INFINITY ? 1.f : __expf(m[i] - m_new);
+            m[i] = m_new;
+            l[i] *= corr[i];
+        }
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[n][e] = s[n][e] == -INFINITY ? 0.f : __expf(s[n][e] - m[e >> 1]);
+                l[e >> 1] += s[n][e];
+            }
+#pragma unroll
+        for (int n = 0; n < NVT; ++n) {
+            acc[n][0] *= corr[0]; acc[n][1] *= corr[0];
+            acc[n][2] *= corr[1]; acc[n][3] *= corr[1];
+        }
+        // ---- 16 rows x all value columns += weights x values; the weights as two bfloat16 halves
+        const bf16* vbase = (SHARED_V ? Ks + (size_t)stage * TM_KT * L.ldk : Vs + (size_t)stage * TM_KT * L.ldv) +
+                            ((lane & 7) + ((lane >> 3) & 1) * 8) * ldvv + (lane >> 4) * 8;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t ah[4], al[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const float w0 = s[2 * kk + (x >> 1)][2 * (x & 1)], w1 = s[2 * kk + (x >> 1)][2 * (x & 1) + 1];
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
+                const float2 back = __bfloat1622float2(hi);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(w0 - back.x, w1 - back.y);
+                ah[x] = *reinterpret_cast<const uint32_t*>(&hi);
+                al[x] = *reinterpret_cast<const uint32_t*>(&lo);
+            }
+#pragma unroll
+            for (int np = 0; np < NVT / 2; ++np) {
+                uint32_t b[4];
+                ldsm_x4_trans(b, vbase + (size_t)kk * 16 * ldvv + np * 16);
+                mma_bf16(acc[2 * np], ah, b[0], b[1]);
+                mma_bf16(acc[2 * np + 1], ah, b[2], b[3]);
+                mma_bf16(acc[2 * np], al, b[0], b[1]);
+                mma_bf16(acc[2 * np + 1], al, b[2], b[3]);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        const int r = warp * 16 + g + 8 * i;
+        if (r >= nrows) continue;
+        const int row = row0 + r;
+        const int tok = qstart + row / group, h = kvh * group + row % group;
+        if (p.nsplit == 1) {
+            const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+            bf16* o = (bf16*)p.out + (size_t)tok * p.out_ld + (size_t)h * dv + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NVT; ++n)
+                *reinterpret_cast<__nv_bfloat162*>(o + n * 8) =
+                    __floats2bfloat162_rn(acc[n][2 * i] * inv, acc[n][2 * i + 1] * inv);
+        } else {
+            const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
+            float* o = p.part_o + idx * dv + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NVT; ++n)
+                *reinterpret_cast<float2*>(o + n * 8) = make_float2(acc[n][2 * i], acc[n][2 * i + 1]);
+            if (t == 0) { p.part_ml[idx * 2] = m[i]; p.part_ml[idx * 2 + 1] = l[i]; }
         }
     }
 }
@@ -614,6 +844,23 @@ static int scaled_attention_mma_launch(const ScaledAttnParams& p, int tiles, boo
     return launch_dependent(scaled_attention_mma_kernel<NV, false>, grid, dim3(SA_WARPS * 32), smem, stream, p);
 }
 
+template <int NVT>
+static int scaled_attention_rows_launch(const ScaledAttnParams& p, int tiles, bool shared_v, cudaStream_t stream) {
+    const size_t smem = RowsLayout(p.key_dim, p.value_dim, shared_v).total;
+    const dim3 grid(p.kv_heads, tiles, p.nsplit);
+    if (shared_v) {
+        cudaFuncSetAttribute(scaled_attention_rows_kernel<NVT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return launch_dependent(scaled_attention_rows_kernel<NVT, true>, grid, dim3(TR_WARPS * 32), smem, stream, p);
+    }
+    cudaFuncSetAttribute(scaled_attention_rows_kernel<NVT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_dependent(scaled_attention_rows_kernel<NVT, false>, grid, dim3(TR_WARPS * 32), smem, stream, p);
+}
+
+// whether the tensor-core form of a warp per 16 rows takes these sizes (value sizes up to 256)
+static bool scaled_attention_rows_takes(int key_dim, int value_dim, bool shared_v) {
+    return value_dim <= 256 && RowsLayout(key_dim, value_dim, shared_v).total <= 227 * 1024;
+}
+
 // whether the tensor-core form takes these sizes and addresses
 static bool scaled_attention_mma_takes(const ScaledAttnParams& p, int dtype, bool shared_v) {
     const int dv = p.value_dim;
@@ -632,9 +879,19 @@ extern "C" {
 
 int fsie_scaled_attention_rows() { return SA_ROWS; }
 
+// Query rows of one tile for these sizes: 64 where a warp of the tensor-core kernel owns 16 rows
+// with all their value columns (bfloat16, key sizes in steps of 16, value sizes 64, 128, 192, 256;
+// form 0 or 2), else 32.  The caller cuts its tile list accordingly.  form 3 asks for the
+// tensor-core kernel whose warps split the value columns at any value size it takes.
+int fsie_scaled_attention_tile_rows(int dtype, int key_dim, int value_dim, int values_in_keys, int form) {
+    if (dtype != DTYPE_BF16 || form == 1 || form == 3 || key_dim % 16 || value_dim % 64) return SA_ROWS;
+    return scaled_attention_rows_takes(key_dim, value_dim, values_in_keys != 0) ? TR_ROWS : SA_ROWS;
+}
+
 // values_in_keys != 0: v_pages is ignored, a key row's first value_dim columns are its value row.
 // form 0: the tensor-core kernel where it takes the sizes (bfloat16), else the 32-bit one; 1: the
-// 32-bit kernel; 2: the tensor-core kernel or refusal.
+// 32-bit kernel; 2: a tensor-core kernel or refusal; 3: the tensor-core kernel whose warps split the
+// value columns, or refusal.  The tiles hold fsie_scaled_attention_tile_rows(...) rows.
 // With nsplit > 1 the caller gives part_o [nsplit, tokens, heads, value_dim] and part_ml
 // [nsplit, tokens, heads, 2] (float); the ranges are merged after the launch.
 int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, const void* k_pages,
@@ -662,7 +919,17 @@ int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, cons
     p.tokens = tokens; p.heads = heads; p.kv_heads = kv_heads; p.window = window; p.nsplit = nsplit;
     p.error = error;
     int rc;
-    if (form != 1 && scaled_attention_mma_takes(p, dtype, values_in_keys != 0)) {
+    const int tile_rows = fsie_scaled_attention_tile_rows(dtype, key_dim, value_dim, values_in_keys, form);
+    if (tile_rows == TR_ROWS) {
+        // the caller has cut tiles of 64 rows: no other kernel may take them
+        if (!scaled_attention_mma_takes(p, dtype, values_in_keys != 0)) return ERR_UNSUPPORTED;
+        switch (value_dim / 64) {
+            case 1: rc = scaled_attention_rows_launch<8>(p, tiles, values_in_keys != 0, stream); break;
+            case 2: rc = scaled_attention_rows_launch<16>(p, tiles, values_in_keys != 0, stream); break;
+            case 3: rc = scaled_attention_rows_launch<24>(p, tiles, values_in_keys != 0, stream); break;
+            default: rc = scaled_attention_rows_launch<32>(p, tiles, values_in_keys != 0, stream); break;
+        }
+    } else if (form != 1 && scaled_attention_mma_takes(p, dtype, values_in_keys != 0)) {
         switch (value_dim / 32) {
             case 2: rc = scaled_attention_mma_launch<2>(p, tiles, values_in_keys != 0, stream); break;
             case 4: rc = scaled_attention_mma_launch<4>(p, tiles, values_in_keys != 0, stream); break;
@@ -671,7 +938,7 @@ int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, cons
             case 12: rc = scaled_attention_mma_launch<12>(p, tiles, values_in_keys != 0, stream); break;
             default: rc = scaled_attention_mma_launch<16>(p, tiles, values_in_keys != 0, stream); break;
         }
-    } else if (form == 2) {
+    } else if (form >= 2) {
         return ERR_UNSUPPORTED;
     } else {
         rc = dtype == DTYPE_F32 ? scaled_attention_dispatch<float>(p, tiles, values_in_keys != 0, stream)

@@ -1119,6 +1119,8 @@ def mixers():
         lib.fsie_gated_act.argtypes = [p, p, ll, i, i, i, p]
         lib.fsie_mingru_scan.argtypes = [p, i, i, p, p, p, i, p, p, i, i, p, p, p, p, i, p]
         lib.fsie_scaled_attention_rows.argtypes = []
+        lib.fsie_scaled_attention_tile_rows.argtypes = [i, i, i, i, i]
+        lib.fsie_scaled_attention_tile_rows.restype = i
         lib.fsie_scaled_attention.argtypes = [p, i, p, p, p, ll, i, i, i, i, p, i, p, p, i, p, p, p, p,
                                               p, i, p, p, i, i, i, i, i, i, i, p, p]
         lib.fsie_rotate_mix_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p,
@@ -1207,8 +1209,17 @@ def mingru_scan(proj: torch.Tensor, width: int, item_qstart: torch.Tensor, item_
     return out
 
 
-def scaled_attention_rows() -> int:
-    return int(mixers().fsie_scaled_attention_rows())
+SCALED_ATTENTION_FORMS = {"auto": 0, "plain": 1, "mma": 2, "mma_split": 3}
+
+
+def scaled_attention_rows(dtype: torch.dtype = torch.float32, key_dim: int = 0, value_dim: int = 0,
+                          values_in_keys: bool = False, form: str = "auto") -> int:
+    """Query rows of one tile of `scaled_attention` for these sizes and this form of the kernel
+    (64 where a warp of the tensor-core kernel owns 16 rows with all their value columns, else 32)."""
+    if key_dim <= 0:
+        return int(mixers().fsie_scaled_attention_rows())
+    return int(mixers().fsie_scaled_attention_tile_rows(_tag(dtype), key_dim, value_dim,
+                                                        int(values_in_keys), SCALED_ATTENTION_FORMS[form]))
 
 
 def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pages: torch.Tensor,
@@ -1223,8 +1234,10 @@ def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pag
     """Causal (optionally windowed) softmax attention of q [tokens, heads x key_dim] over paged keys
     [kv_head][slot][key_dim] and values [kv_head][slot][value_dim] (or, values_in_keys, the first
     value_dim columns of the key rows), scores multiplied by head_scale[head]; scores, softmax and
-    weights in 32-bit.  `form`: "auto" takes the tensor-core kernel where it fits (bfloat16, key
-    sizes in steps of 16, value sizes 64 ... 512), "plain" the 32-bit kernel, "mma" insists."""
+    weights in 32-bit.  `form`: "auto" takes a tensor-core kernel where one fits (bfloat16, key
+    sizes in steps of 16, value sizes 64 ... 512), "plain" the 32-bit kernel, "mma" insists on a
+    tensor-core kernel, "mma_split" on the one whose warps split the value columns.  The tiles
+    hold `scaled_attention_rows(dtype, key_dim, value_dim, values_in_keys, form)` rows."""
     _need(q, None, "q", contiguous=False)
     _need(head_scale, torch.float32, "head_scale")
     _need(out, q.dtype, "out")
@@ -1241,7 +1254,7 @@ def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pag
         value_dim, int(values_in_keys), _ptr(block_tables), block_tables.stride(0), _ptr(tile_item),
         _ptr(tile_row0), tiles, _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots),
         _ptr(out), heads * value_dim, _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, window,
-        nsplit, _tag(q.dtype), {"auto": 0, "plain": 1, "mma": 2}[form], _ptr(error), _stream()),
+        nsplit, _tag(q.dtype), SCALED_ATTENTION_FORMS[form], _ptr(error), _stream()),
         "scaled_attention")
     return out
 

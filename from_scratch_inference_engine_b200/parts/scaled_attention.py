@@ -31,9 +31,11 @@ def attend(ctx, rt, q: torch.Tensor, head_scale: torch.Tensor, group, cache: Lay
     """The step's tokens over the pages through `ops.scaled_attention`: tiles of query rows, key
     ranges split over blocks when the tiles are few."""
     tokens = q.shape[0]
-    tiles = ctx.attention_tiles(heads // kv_heads, ops.scaled_attention_rows())
-    longest = ctx.max_context if window <= 0 else min(ctx.max_context, window + ops.scaled_attention_rows())
-    nsplit = key_splits(tiles.count * kv_heads, longest, rt.sm_count)
+    rows = ops.scaled_attention_rows(q.dtype, key_dim, value_dim, values_in_keys)
+    tiles = ctx.attention_tiles(heads // kv_heads, rows)
+    longest = ctx.max_context if window <= 0 else min(ctx.max_context, window + rows)
+    nsplit = key_splits(tiles.count * kv_heads, longest, rt.sm_count,
+                        key_tile=64 if q.dtype is torch.bfloat16 else 32)
     part_o = part_ml = None
     if nsplit > 1:
         part_o = ctx.scratch("scaled_attention.part_o", nsplit * tokens * heads * value_dim)

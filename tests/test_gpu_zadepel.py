@@ -226,7 +226,7 @@ def test_scaled_attention_far_keys_page_borders_and_window_edges(dtype, window, 
         dk, dv = 24, (16 if shared else 40)
     else:
         dk, dv = (80, 64) if shared else (48, 128)
-    forms = ["plain", "mma"] if sizes != "small" and dtype is torch.bfloat16 else ["auto"]
+    forms = ["plain", "mma", "mma_split"] if sizes != "small" and dtype is torch.bfloat16 else ["auto"]
     group = heads // kv_heads
     lengths = [(300, 77), (260, 1)]
     pages_total = sum(-(-(a + b) // page) for a, b in lengths) + 3
@@ -265,17 +265,17 @@ def test_scaled_attention_far_keys_page_borders_and_window_edges(dtype, window, 
         bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
     q = torch.cat(qs).reshape(-1, heads * dk).cuda()
     tokens = q.shape[0]
-    item, row0 = [], []
-    for i, (_, new) in enumerate(lengths):
-        for r in range(0, new * group, ops.scaled_attention_rows()):
-            item.append(i)
-            row0.append(r)
     dev = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
     # a page holds its keys and then, unless they live in the key rows, its values
     both = (k_pages if shared else torch.cat([k_pages, v_pages], dim=1)).cuda()
     keys = kv_heads * page * dk
     expect = torch.cat(want)
     for nsplit, form in [(n, f) for n in (1, 5) for f in forms]:
+        item, row0 = [], []                    # the tiles of query rows this form of the kernel takes
+        for i, (_, new) in enumerate(lengths):
+            for r in range(0, new * group, ops.scaled_attention_rows(dtype, dk, dv, shared, form)):
+                item.append(i)
+                row0.append(r)
         out = torch.zeros(tokens, heads * dv, device="cuda", dtype=dtype)
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
         ops.scaled_attention(q, heads * dk, head_scale.float().cuda(), both[:, :keys],
