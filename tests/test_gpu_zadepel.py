@@ -394,6 +394,26 @@ def test_latent_rows_and_products_per_head(dtype):
                           torch.einsum("thr,tr->th", want_over, c))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,heads,n,k", [(70, 3, 20, 10), (9, 2, 100, 24), (1, 4, 64, 512), (16, 2, 33, 7),
+                                              (150, 3, 72, 32), (300, 2, 512, 136), (64, 1, 64, 64)])
+def test_product_per_head_in_its_three_forms(dtype, tokens, heads, n, k):
+    """out[t, h] = W[h] x[t, h] through the kernel for few tokens, the tensor-core kernel (bfloat16,
+    k in steps of 8) and the plain one; rows of x and out that lie inside wider rows."""
+    from from_scratch_inference_engine_b200.kernels import ops
+    g = torch.Generator().manual_seed(tokens + n)
+    x_head, out_head = k + 8, n + 16
+    x = torch.randn(tokens, heads * x_head, generator=g).to(dtype)
+    w = (torch.randn(heads, n, k, generator=g) / k ** 0.5).to(dtype)
+    out = torch.full((tokens, heads * out_head), 7.0, dtype=dtype, device="cuda")
+    ops.head_product(x.cuda(), heads * x_head, x_head, w.cuda(), out, heads * out_head, out_head, tokens)
+    want = torch.einsum("thk,hnk->thn", x.double().reshape(tokens, heads, x_head)[..., :k], w.double())
+    got = out.cpu().double().reshape(tokens, heads, out_head)
+    tolerance = 1e-5 if dtype is torch.float32 else 1e-2
+    assert (got[..., :n] - want).abs().max() < tolerance * max(1.0, float(want.abs().max()))
+    assert float(got[..., n:].min()) == 7.0 and float(got[..., n:].max()) == 7.0      # nothing beyond a head's columns
+
+
 def test_cache_entry_of_latent_rows():
     """A latent layer's cache entry keeps one row per token and nothing beside it; its pages go
     back behind the window."""
