@@ -48,19 +48,34 @@ __global__ void mingru_scan_kernel(const T* __restrict__ proj, int ld, int width
     if (MODE == 0) s = state[(size_t)slot * width + c];
     if (MODE == 2) s = seg_start[(size_t)unit * width + c];
     T* o = MODE == 1 ? nullptr : out + (size_t)(item_qstart[item] + first) * width + c;
-    for (int t = 0; t < count; ++t) {
-        const float a = to_float(row[0]), u = to_float(row[width]);
-        float z, cand;
-        mingru_gates(a, u, z, cand);
-        s = (1.0f - z) * s + z * cand;
-        if (MODE == 1) {
-            carry *= 1.0f - z;
-        } else {
-            const float g = to_float(row[2 * width]);
-            o[0] = from_float<T>(s * (g / (1.0f + expf(-g))));
-            o += width;
+    // eight tokens' values are asked for before the first is used: the loads do not depend on the
+    // recurrence, only the sums do
+    constexpr int AHEAD = 8;
+    for (int t0 = 0; t0 < count; t0 += AHEAD) {
+        T av[AHEAD], uv[AHEAD], gv[AHEAD];
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            const bool in = t0 + j < count;
+            const T* r = row + (size_t)(in ? j : 0) * ld;
+            av[j] = r[0];
+            uv[j] = r[width];
+            if (MODE != 1) gv[j] = r[2 * width];
         }
-        row += ld;
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            if (t0 + j >= count) break;
+            float z, cand;
+            mingru_gates(to_float(av[j]), to_float(uv[j]), z, cand);
+            s = (1.0f - z) * s + z * cand;
+            if (MODE == 1) {
+                carry *= 1.0f - z;
+            } else {
+                const float g = to_float(gv[j]);
+                o[0] = from_float<T>(s * (g / (1.0f + expf(-g))));
+                o += width;
+            }
+        }
+        row += (size_t)AHEAD * ld;
     }
     if (MODE == 0 || (MODE == 2 && first + count >= qlen)) state[(size_t)slot * width + c] = s;
     if (MODE == 1) {

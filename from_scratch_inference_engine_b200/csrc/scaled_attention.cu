@@ -270,7 +270,8 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
     float* psum = pmax + SA_ROWS * 4;                                              // [32][4]
     int* key_ok = reinterpret_cast<int*>(psum + SA_ROWS * 4);                      // [2][64]
 
-    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
+    // blocks start in the order of the grid: the last tiles of a prompt see the most keys and go first
+    const int kvh = blockIdx.x, tile = gridDim.y - 1 - blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     grid_dependency_wait();
     grid_dependents_go();
@@ -303,17 +304,18 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
 
     // one tile of keys (and values) on its way into slot `stage`: THREADS / 64 threads share a row, so
     // that all 64 page lookups are under way at once
-    auto issue_tile = [&](int stage, int k0) {
+    // the page of this thread's key in the tile that starts at k0 (asked for a tile ahead of its use)
+    auto page_of = [&](int k0) {
+        const int kj = k0 + tid / ((SA_WARPS * 32) / TM_KT);
+        return kj < kend ? bt[kj / p.page_size] : -1;
+    };
+    auto issue_tile = [&](int stage, int k0, int page) {
         constexpr int TPR = (SA_WARPS * 32) / TM_KT;
         const int j = tid / TPR, part = tid % TPR;
         const int kj = k0 + j;
-        int page = -1;
-        if (kj < kend) {
-            page = bt[kj / p.page_size];
-            if (page < 0 && part == 0 && p.error && kj <= pos_last &&
-                (p.window <= 0 || kj > pos_first - p.window))
-                atomicExch(p.error, 3);            // some row of the tile sees this key, and its page was given back
-        }
+        if (kj < kend && page < 0 && part == 0 && p.error && kj <= pos_last &&
+            (p.window <= 0 || kj > pos_first - p.window))
+            atomicExch(p.error, 3);                // some row of the tile sees this key, and its page was given back
         const bool ok = page >= 0;
         const long long at = (long long)kvh * p.page_size + kj % p.page_size;
         const bf16* ksrc = kp + (ok ? (long long)page * p.page_stride + at * dk : 0);
@@ -327,7 +329,8 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
         if (part == 0) key_ok[stage * TM_KT + j] = ok;
         cp_async_commit();
     };
-    if (kbegin < kend) issue_tile(0, kbegin);
+    if (kbegin < kend) issue_tile(0, kbegin, page_of(kbegin));
+    int page_ahead = page_of(kbegin + TM_KT);
 
     // the tile's query rows as they are (the head's scale meets the scores), zero beyond the tile
     for (int r = warp; r < SA_ROWS; r += SA_WARPS) {
@@ -361,7 +364,10 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
         const int stage = it & 1;
         cp_async_wait_all();
         __syncthreads();                 // this tile has arrived; everybody is done with the tile before it
-        if (k0 + TM_KT < kend) issue_tile(stage ^ 1, k0 + TM_KT);
+        if (k0 + TM_KT < kend) {
+            issue_tile(stage ^ 1, k0 + TM_KT, page_ahead);
+            page_ahead = page_of(k0 + 2 * TM_KT);
+        }
         // ---- scores of 16 rows x 16 keys over the whole key size
         float s[2][4];
 #pragma unroll
@@ -518,7 +524,8 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
     bf16* Vs = reinterpret_cast<bf16*>(tr_smem + L.q_bytes + L.k_bytes);           // [2][64][ldv]
     int* key_ok = reinterpret_cast<int*>(tr_smem + L.q_bytes + L.k_bytes + L.v_bytes);   // [2][64]
 
-    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
+    // blocks start in the order of the grid: the last tiles of a prompt see the most keys and go first
+    const int kvh = blockIdx.x, tile = gridDim.y - 1 - blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     grid_dependency_wait();
     grid_dependents_go();
@@ -550,17 +557,18 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
 
     // one tile of keys (and values) on its way into slot `stage`: THREADS / 64 threads share a row, so
     // that all 64 page lookups are under way at once
-    auto issue_tile = [&](int stage, int k0) {
+    // the page of this thread's key in the tile that starts at k0 (asked for a tile ahead of its use)
+    auto page_of = [&](int k0) {
+        const int kj = k0 + tid / ((TR_WARPS * 32) / TM_KT);
+        return kj < kend ? bt[kj / p.page_size] : -1;
+    };
+    auto issue_tile = [&](int stage, int k0, int page) {
         constexpr int TPR = (TR_WARPS * 32) / TM_KT;
         const int j = tid / TPR, part = tid % TPR;
         const int kj = k0 + j;
-        int page = -1;
-        if (kj < kend) {
-            page = bt[kj / p.page_size];
-            if (page < 0 && part == 0 && p.error && kj <= pos_last &&
-                (p.window <= 0 || kj > pos_first - p.window))
-                atomicExch(p.error, 3);            // some row of the tile sees this key, and its page was given back
-        }
+        if (kj < kend && page < 0 && part == 0 && p.error && kj <= pos_last &&
+            (p.window <= 0 || kj > pos_first - p.window))
+            atomicExch(p.error, 3);                // some row of the tile sees this key, and its page was given back
         const bool ok = page >= 0;
         const long long at = (long long)kvh * p.page_size + kj % p.page_size;
         const bf16* ksrc = kp + (ok ? (long long)page * p.page_stride + at * dk : 0);
@@ -574,7 +582,8 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
         if (part == 0) key_ok[stage * TM_KT + j] = ok;
         cp_async_commit();
     };
-    if (kbegin < kend) issue_tile(0, kbegin);
+    if (kbegin < kend) issue_tile(0, kbegin, page_of(kbegin));
+    int page_ahead = page_of(kbegin + TM_KT);
 
     for (int r = warp; r < TR_ROWS; r += TR_WARPS) {
         const int row = row0 + r;
@@ -609,7 +618,10 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
         const int stage = it & 1;
         cp_async_wait_all();
         __syncthreads();                 // this tile has arrived; everybody is done with the tile before it
-        if (k0 + TM_KT < kend) issue_tile(stage ^ 1, k0 + TM_KT);
+        if (k0 + TM_KT < kend) {
+            issue_tile(stage ^ 1, k0 + TM_KT, page_ahead);
+            page_ahead = page_of(k0 + 2 * TM_KT);
+        }
         if (k0 > warp_last || (p.window > 0 && k0 + TM_KT - 1 <= warp_first - p.window)) continue;
         // ---- scores of 16 rows x 64 keys
         float s[8][4];
