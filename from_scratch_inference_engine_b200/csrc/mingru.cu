@@ -95,12 +95,27 @@ __global__ void mingru_chain_kernel(const int* __restrict__ item_slots, const in
     grid_dependency_wait();
     grid_dependents_go();
     float s = 0.f;
-    for (int seg = 0; seg < num_segs; ++seg) {
-        const int slot = item_slots[seg_item[seg]];
-        if (slot < 0) continue;
-        if (seg_row0[seg] == 0) s = state[(size_t)slot * width + c];
-        seg_start[(size_t)seg * width + c] = s;
-        s = seg_ab[((size_t)seg * 2) * width + c] * s + seg_ab[((size_t)seg * 2 + 1) * width + c];
+    // eight segments' (A, B), slots and first rows are asked for before the chain through them runs
+    constexpr int AHEAD = 8;
+    for (int seg0 = 0; seg0 < num_segs; seg0 += AHEAD) {
+        float a[AHEAD], b[AHEAD];
+        int slot[AHEAD], row0[AHEAD];
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            const int seg = min(seg0 + j, num_segs - 1);
+            a[j] = seg_ab[((size_t)seg * 2) * width + c];
+            b[j] = seg_ab[((size_t)seg * 2 + 1) * width + c];
+            slot[j] = item_slots[seg_item[seg]];
+            row0[j] = seg_row0[seg];
+        }
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            if (seg0 + j >= num_segs) break;
+            if (slot[j] < 0) continue;
+            if (row0[j] == 0) s = state[(size_t)slot[j] * width + c];
+            seg_start[(size_t)(seg0 + j) * width + c] = s;
+            s = a[j] * s + b[j];
+        }
     }
 }
 
