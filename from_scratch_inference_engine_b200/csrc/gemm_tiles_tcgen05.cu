@@ -62,7 +62,7 @@ constexpr uint32_t FIRST_BLOCK_MASK = 0xFEFFFFFFu;       // clears the bit of a 
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 
-// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+// g/2 * (1 + tanh(0.7978845608 * (g + 0.044715 g^3)))
 __device__ __forceinline__ float gelu_tanh_gate(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }

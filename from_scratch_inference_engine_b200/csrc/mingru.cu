@@ -1,7 +1,8 @@
-// minGRU: a gated recurrence, element by element, whose gates read only the current token.
+// minGRU: an element-wise recurrence; gate and candidate of a token come from that token's
+// projections alone, never from the state.
 //
 //   proj[t] = [ a | u | g ]  (three blocks of `width` columns: the product's result, biases added)
-//   z = sigmoid(a);   cand = u + 1/2 where u >= 0, sigmoid(u) where u < 0
+//   z = sigmoid(a);   cand = (u < 0) ? sigmoid(u) : u + 0.5
 //   S_t = (1 - z) S_{t-1} + z cand            (S: float32 [width] in the request's state slot)
 //   out[t] = T( S_t * silu(g) )
 //

@@ -9,7 +9,7 @@
 //   the storage type T of delta and y.
 //
 //   gated_act:       act[t, i] = f(gu[t, i]) * gu[t, inter + i],  f = SiLU or the tanh form of GELU,
-//                    0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in 32-bit.
+//                    g/2 * (1 + tanh(0.7978845608 * (g + 0.044715 g^3))), in 32-bit.
 #include "common.cuh"
 #include <math.h>
 

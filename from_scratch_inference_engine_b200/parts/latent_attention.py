@@ -1,5 +1,5 @@
-"""Attention over a cache of latent rows: per token one normed low-rank vector and one rotated key
-part shared by all heads."""
+"""Attention over a cache of latent rows: per token one normed low-rank vector and a single rotated
+key vector that every head uses."""
 
 from __future__ import annotations
 
@@ -18,9 +18,9 @@ from .scaled_attention import attend
 @register_part("mixer", "latent_attention")
 class LatentAttention(Mixer):
     """q = W_q y, per head [dim unrotated | rope rotated].  W_dkv y = [lat (rank) | kr (rope)]:
-    c = rms_norm(lat) * gain is the latent, kr one rotated key part shared by all heads.  Head h
+    c = rms_norm(lat) * gain is the latent, kr a single rotated key vector that every head uses.  Head h
     has keys [U_h c | kr] and values V_h c (W_uk = U, W_uv = V stacked head by head); scores
-    (q . k) * scale over the keys 0 <= i - j < window (all j <= i without a window); softmax;
+    (q . k) * scale over the keys j in (i - window, i] (all j <= i without a window); softmax;
     output projection on the concatenated heads.  Rotation by `position` (pairs 2i, 2i + 1) over
     the first rotary_dim columns of a rope part.
 

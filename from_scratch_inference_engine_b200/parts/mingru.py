@@ -1,4 +1,5 @@
-"""minGRU: a gated recurrence over per-request state whose gates read only the current token."""
+"""minGRU: an element-wise recurrence over per-request state; gate and candidate of a token come
+from that token's projections alone."""
 
 from __future__ import annotations
 
@@ -13,9 +14,10 @@ from .base import LayerCache, Mixer, StateNeed, register_part
 
 @register_part("mixer", "mingru")
 class MinGru(Mixer):
-    """z = sigmoid(W_z y + b_z) and u = W_x y + b_x, both `width` wide; the candidate is u + 1/2
-    where u >= 0 and sigmoid(u) where u < 0; element by element S_t = (1 - z) S_{t-1} + z cand;
-    the output is W_o (S_t * silu(W_g y)).
+    """With a = W_z y + b_z and u = W_x y + b_x (`width` channels each): z = sigmoid(a),
+    cand = sigmoid(u) for negative u and u + 0.5 otherwise, and per channel
+    S_t = S_{t-1} + z (cand - S_{t-1}), written as (1 - z) S_{t-1} + z cand; the mixer returns
+    W_o (S_t * silu(W_g y)).
 
     The state S [width] is float32, zero when a request starts, and lives in the request's state
     slot; gates, candidate and state are computed in 32-bit.  The three projections are one

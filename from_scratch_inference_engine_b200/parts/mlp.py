@@ -15,7 +15,7 @@ from .base import Part, register_part
 @register_part("feed_forward", "swiglu")
 class SwiGluMlp(Part):
     """down( act(gate(y)) * up(y) ) with act = SiLU unless `activation` names another
-    ("gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), without biases (reference: src/model/model.cpp:136-140,
+    ("gelu_tanh": g/2 * (1 + tanh(0.7978845608 * (g + 0.044715 g^3)))), without biases (reference: src/model/model.cpp:136-140,
     src/model/nn.cpp:74-88) or, with `bias`, with one on each of the three projections.  gate
     and up are one product over the stacked weight [2 * intermediate, hidden]: gate rows first,
     then up rows.  `names` gives the tensor names below the prefix: the three projections, and

@@ -10,12 +10,13 @@ The design in this file's notation (h: input of a sublayer, rows are tokens, p: 
     latent     q = W_q h, per head [nope | rope];  d = W_dkv h = [lat | kr];  c = N(lat) * w_c
                k_nope[head] = W_uk[head] c,  v[head] = W_uv[head] c;  kr is rotated and shared by
                all heads;  s = (q_nope . k_nope + rot(q_rope) . rot(kr)) * scale  over the keys
-               0 <= i - j < size;  softmax;  out = W_o concat(heads)
+               j in (i - size, i];  softmax;  out = W_o concat(heads)
                rot here: interleaved pairs (2i, 2i+1), angle p * base^(-2i/dims)
     attention  q, k, v = W h + b;  rot: pairs (i, i + dims/2) of the first `dims` of a head;
                s = (q . k) * scale * temp[head] over j <= i;  softmax;  head h reads key/value
                head h // (heads / kv_heads);  in every value-mixing layer but the first,
-               v <- (1 - m) v + m v_first with v_first the first such layer's v of the token
+               v <- (1 - m) v + m v_src, v_src being what the first of those layers computed as v
+               for the same token
     mingru     z = sigmoid(W_z h + b_z);  u = W_x h + b_x;  cand = u + 1/2 (u >= 0), sigmoid(u) (u < 0)
                S_p = (1 - z) S_{p-1} + z cand  (S_{-1} = 0);  out = W_o(S_p * silu(W_g h))
     ff         W_down(gelu_tanh(W_gate h) * (W_up h))

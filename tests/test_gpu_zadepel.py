@@ -616,3 +616,31 @@ def test_llm_entry_point_reads_the_design_by_its_name(tmp_path_factory):
         logits = plain.forward(config, weights, seq)[-1]
         assert float(logits.max() - logits[token]) <= 1e-3 * max(1.0, float(logits.abs().max()))
         seq.append(token)
+
+
+@pytest.mark.parametrize("dtype,name,bound", [("float32", "hybrid", F32_BOUND), ("bfloat16", "wide", BF16_BOUND)])
+def test_trace_replay_program_runs_the_design(tmp_path_factory, tmp_path, dtype, name, bound):
+    """bin/trace_run as a user runs it (a subprocess, steps on standard input, logits in files)
+    on a mixed trace of five requests through four slots and a pool for the live tokens only."""
+    import json
+    import subprocess
+    from pathlib import Path
+    folder = folder_of(tmp_path_factory, name, sharpen=SHARPEN[dtype])
+    vocab = vocab_of(name)
+    requests = {key: helpers.random_ids(vocab, n, i)
+                for i, (key, n) in enumerate({"a": 90, "b": 40, "c": 70, "d": 33, "e": 64}.items())}
+    steps = helpers.trace_mixed(requests, seed=3)
+    need = helpers.live_tokens_needed(steps, round_to=64)
+    root = Path(__file__).resolve().parent.parent
+    text = "".join(json.dumps(step) + "\n" for step in steps)
+    done = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
+                           "--out", str(tmp_path / "out"), "--max-tokens", str(need)],
+                          input=text, capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [line for line in done.stdout.splitlines() if line.startswith("done ")] == \
+        [f"done {s['step']}" for s in steps]
+    outputs = {s["step"]: np.fromfile(tmp_path / "out" / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab)
+               for s in steps if any(e["want"] for e in s["entries"])}
+    rows = helpers.collect_rows(steps, outputs)
+    assert len(rows) == sum(len(ids) for ids in requests.values())
+    assert_rows(rows, requests, folder, bound)
