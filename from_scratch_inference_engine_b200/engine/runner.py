@@ -279,8 +279,8 @@ class ModelRunner:
     # --------------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry],
              device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-        """Run one batch; returns float32 logits [wanted places, vocab] in the order of the
-        entries and of their `want`, or None when nothing is wanted.  The returned tensor
+        """Run one batch; returns float32 logits [wanted places, vocab], entry by entry and within an
+        entry as its `want` lists the places, or None when nothing is wanted.  The returned tensor
         may be reused by the next step: read it before stepping again.  `device_tokens`
         (int32, on the device) holds the tokens of entries with a `source_row`."""
         self._validate(entries)
