@@ -14,6 +14,9 @@ from ..weights.tensor_spec import TensorSpec
 from .base import LayerCache, Mixer, build_part, register_part
 
 MAX_KEY_SPLITS = 64
+# which form of the attention kernel `attend` asks for: "auto" (a tensor-core kernel where one takes
+# the sizes), or "plain" to measure or test the 32-bit kernel in its place
+FORM = "auto"
 
 
 def key_splits(blocks: int, longest: int, sms: int, key_tile: int = 32) -> int:
@@ -31,7 +34,7 @@ def attend(ctx, rt, q: torch.Tensor, head_scale: torch.Tensor, group, cache: Lay
     """The step's tokens over the pages through `ops.scaled_attention`: tiles of query rows, key
     ranges split over blocks when the tiles are few."""
     tokens = q.shape[0]
-    rows = ops.scaled_attention_rows(q.dtype, key_dim, value_dim, values_in_keys)
+    rows = ops.scaled_attention_rows(q.dtype, key_dim, value_dim, values_in_keys, FORM)
     tiles = ctx.attention_tiles(heads // kv_heads, rows)
     longest = ctx.max_context if window <= 0 else min(ctx.max_context, window + rows)
     nsplit = key_splits(tiles.count * kv_heads, longest, rt.sm_count,
@@ -45,7 +48,7 @@ def attend(ctx, rt, q: torch.Tensor, head_scale: torch.Tensor, group, cache: Lay
                                 values_in_keys, group.block_tables, tiles.item, tiles.row0,
                                 tiles.count, ctx.item_qstart, ctx.item_qlen, ctx.item_pos0,
                                 ctx.item_slots, out, tokens, heads, kv_heads, window, ctx.error,
-                                nsplit, part_o, part_ml)
+                                nsplit, part_o, part_ml, form=FORM)
 
 
 @register_part("mixer", "scaled_gqa_attention")
